@@ -1,0 +1,179 @@
+/*
+ * pa_decode_sm100.h -- C ABI of the B200 (sm_100a) paged-attention decode operator.
+ *
+ * The library replaces one operator of yanguahe/triton_op: the split-KV paged-attention
+ * decode ("v2") and its cross-partition log-sum-exp reduce.  Every entry point takes plain
+ * device pointers, sizes and strides; nothing here knows about torch.  All pointers are
+ * device pointers unless stated otherwise, are borrowed for the duration of the call only,
+ * and nothing is allocated or freed by the library.  Every function returns PA_OK (0) or a
+ * negative PaStatus, never throws, never prints, never exits.  Calls are asynchronous on the
+ * given stream and re-entrant (the only global state is a per-device attribute cache).
+ *
+ * Reference interface replaced (paths inside yanguahe/triton_op):
+ *   pa_decode_triton_gluon_fp8.py:1659-1897   paged_attention_decode        -> pa_decode_sm100
+ *   pa_decode_triton_gluon_fp8.py:514-1002    paged_attention_decode_v2_gluon_fp8 (block 16/64)
+ *   pa_decode_triton_gluon_fp8.py:27-501      ..._large_block_fp8 (block 1024) -> pa_partition_sm100
+ *   pa_decode_triton_gluon_fp8.py:1187-1333   paged_attention_decode_v2_reduce_kernel -> pa_reduce_sm100
+ *   pa_decode_gluon.py:655-756                bf16-KV paged_attention_decode (same entry, kv_dtype = PA_DT_BF16)
+ */
+#ifndef PA_DECODE_SM100_H
+#define PA_DECODE_SM100_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PA_ABI_VERSION 1
+
+typedef enum PaStatus {
+  PA_OK = 0,
+  PA_ERR_NULL_POINTER = -1,   /* a required pointer is NULL */
+  PA_ERR_BAD_SHAPE = -2,      /* a size is zero/negative or sizes disagree */
+  PA_ERR_UNSUPPORTED = -3,    /* shape or dtype combination the kernels do not cover */
+  PA_ERR_ALIGNMENT = -4,      /* a pointer or stride breaks the 16-byte rule of the bulk copies */
+  PA_ERR_CUDA = -5,           /* a CUDA runtime call failed (see pa_last_cuda_error) */
+  PA_ERR_ABI = -6,            /* struct_size does not match this library */
+  PA_ERR_TOO_LARGE = -7       /* a size exceeds a stated fixed limit */
+} PaStatus;
+
+typedef enum PaDType {
+  PA_DT_BF16 = 0,
+  PA_DT_E4M3FN = 1            /* OCP e4m3fn, max 448 */
+} PaDType;
+
+/* Quantisation mode of a scale argument; the values are the reference's own
+ * (pa_decode_triton_gluon_fp8.py:1752-1790). */
+typedef enum PaQuantMode {
+  PA_QUANT_NONE = -1,         /* no scale */
+  PA_QUANT_PER_TENSOR = 0,    /* pointer to ONE fp32 in device memory */
+  PA_QUANT_PER_TOKEN = 1      /* [num_blocks, num_kv_heads, block_size] fp32, last dim contiguous */
+} PaQuantMode;
+
+/* Value-cache layouts (pa_decode_triton_gluon_fp8.py:1792-1799). */
+typedef enum PaVLayout {
+  PA_V_NORMAL = 0,            /* [num_blocks, num_kv_heads, head_size, block_size] */
+  PA_V_TRANSPOSED = 1         /* [num_blocks, num_kv_heads, block_size/x, head_size, x] */
+} PaVLayout;
+
+/* Bits the kernels may OR into *status (device int32, optional). 0 means a clean run. */
+#define PA_DEV_WAIT_TIMEOUT   1  /* a bounded wait on a bulk copy ran out; results are undefined */
+#define PA_DEV_BAD_PAGE_ID    2  /* a block-table entry was outside [0, num_blocks); it was clamped */
+#define PA_DEV_CTX_TOO_LONG   4  /* a context length exceeded max_blocks_per_seq*block_size; it was clamped */
+
+/*
+ * One decode call.  Symbols: S num_seqs, Hkv num_kv_heads, G query heads per kv head,
+ * L query_len (MTP), eqG = L*G, D head_size (128), bs block_size, P max_partitions,
+ * x = 16/itemsize(kv).
+ *
+ * Row order inside one kv head follows the reference (test_pa_mtp.py:793-822): query row
+ * r = t*G + g holds new token t (0..L-1) of head g; row r attends key j iff
+ * (L-1-t) + j < context_len (pa_decode_triton_gluon_fp8.py:915-920).
+ */
+typedef struct PaDecodeParams {
+  uint32_t struct_size;        /* = sizeof(PaDecodeParams) */
+  uint32_t abi_version;        /* = PA_ABI_VERSION */
+
+  /* tensors */
+  void* out;                   /* [S, Hkv*eqG, D] out_dtype; written in place */
+  const void* query;           /* [S, Hkv*eqG, D] q_dtype; last dim contiguous */
+  const void* key_cache;       /* [NB, Hkv, D/x, bs, x]; the last three dims contiguous */
+  const void* value_cache;     /* PA_V_NORMAL: [NB, Hkv, D, bs]; the last two dims contiguous */
+  const int32_t* block_tables; /* [S, max_blocks_per_seq] */
+  const int32_t* context_lens; /* [S] */
+  const float* query_scale;    /* per-tensor [1] / per-token [S, Hkv*eqG]; NULL when PA_QUANT_NONE */
+  const float* key_scale;      /* per-tensor [1] / per-token [NB, Hkv, bs]; NULL when PA_QUANT_NONE */
+  const float* value_scale;    /* same shape as key_scale */
+  const float* alibi_slopes;   /* [Hkv*G] or NULL */
+
+  /* workspaces, caller-owned (reference: torch.zeros at pa_decode_triton_gluon_fp8.py:1729-1733).
+   * They need not be zeroed: every partition the reduce reads is written by the partition kernel. */
+  float* exp_sums;             /* [S, Hkv, P, eqG] fp32 */
+  float* max_logits;           /* [S, Hkv, P, eqG] fp32 */
+  void* tmp_out;               /* [S, Hkv, P, eqG, D] out_dtype, already divided by exp_sums */
+  int32_t* status;             /* optional device int32, OR-ed with PA_DEV_* bits */
+
+  /* sizes */
+  int32_t num_seqs;            /* S */
+  int32_t num_kv_heads;        /* Hkv */
+  int32_t query_group_size;    /* G */
+  int32_t query_len;           /* L, 1..4 */
+  int32_t head_size;           /* D, must be 128 */
+  int32_t block_size;          /* bs: 16, 64 or 1024 */
+  int32_t num_blocks;          /* NB */
+  int32_t max_blocks_per_seq;  /* columns of block_tables */
+  int32_t partition_size;      /* tokens per split-KV partition: 256 (reference constant) or 512 */
+  int32_t max_partitions;      /* P, the partition extent of the workspaces */
+
+  /* strides, in ELEMENTS of the tensor's dtype */
+  int64_t out_stride_seq, out_stride_head;
+  int64_t q_stride_seq, q_stride_head;
+  int64_t k_stride_block, k_stride_head;
+  int64_t v_stride_block, v_stride_head;
+  int64_t bt_stride_seq;
+  int64_t q_scale_stride_seq;              /* per-token query scale only */
+  int64_t kv_scale_stride_block, kv_scale_stride_head;  /* per-token kv scales only */
+  int64_t ws_stride_seq, ws_stride_head, ws_stride_part;                   /* exp_sums / max_logits */
+  int64_t tmp_stride_seq, tmp_stride_head, tmp_stride_part, tmp_stride_row;/* tmp_out */
+
+  /* dtypes and modes */
+  int32_t q_dtype;             /* PaDType */
+  int32_t kv_dtype;            /* PaDType */
+  int32_t out_dtype;           /* PaDType; PA_DT_BF16 */
+  int32_t q_quant_mode;        /* PaQuantMode */
+  int32_t kv_quant_mode;       /* PaQuantMode */
+  int32_t v_layout;            /* PaVLayout */
+  float softmax_scale;
+
+  /* 0 = library default.  tune_warps: consumer warps per CTA; tune_stages: ring depth per
+   * warp; tune_ctas: grid size.  For benchmarking sweeps; results do not depend on them. */
+  int32_t tune_warps, tune_stages, tune_ctas, reserved0;
+} PaDecodeParams;
+
+/* Partition kernel followed by the reduce kernel on `stream` (a cudaStream_t). */
+int pa_decode_sm100(const PaDecodeParams* params, void* stream);
+
+/* The partition kernel alone: fills exp_sums / max_logits / tmp_out, leaves `out` untouched. */
+int pa_partition_sm100(const PaDecodeParams* params, void* stream);
+
+/*
+ * The reduce kernel alone: merges the partitions in the workspaces into `out`.
+ * When tri_m / tri_l / tri_o are all non-NULL it ALSO stores the merged (max, sum, normalised
+ * output) triple of every output row in fp32 -- the unit the multi-GPU merge exchanges:
+ *   tri_m, tri_l: [S*Hkv*eqG]; tri_o: [S*Hkv*eqG, D].  Row index = seq*(Hkv*eqG) + head*eqG + r.
+ * `out` may be NULL in that case.
+ */
+int pa_reduce_sm100(const PaDecodeParams* params, float* tri_m, float* tri_l, float* tri_o,
+                    void* stream);
+
+/*
+ * Cross-shard log-sum-exp merge (no counterpart in the single-GPU reference; it is the
+ * reduce of pa_decode_triton_gluon_fp8.py:1187-1333 applied across GPUs instead of partitions).
+ *   m, l : [num_shards, num_rows] fp32      o : [num_shards, num_rows, head_size] fp32
+ *   out  : [num_rows, head_size] bf16 with row stride out_stride_row (elements)
+ *   out[r] = sum_g o[g,r]*l[g,r]*exp(m[g,r]-M[r]) / sum_g l[g,r]*exp(m[g,r]-M[r]),  M = max_g m
+ * Shards with l == 0 contribute nothing.
+ */
+int pa_merge_triples_sm100(void* out, int64_t out_stride_row, const float* m, const float* l,
+                           const float* o, int32_t num_shards, int32_t num_rows, int32_t head_size,
+                           void* stream);
+
+/* Bytes of dynamic shared memory and the grid the partition kernel would use for `params`
+ * (host-only query, launches nothing).  Any output pointer may be NULL. */
+int pa_query_launch_sm100(const PaDecodeParams* params, int32_t* grid_ctas, int32_t* cta_threads,
+                          int32_t* smem_bytes, int32_t* ring_stages);
+
+/* Static string for a PaStatus. */
+const char* pa_strerror(int status);
+
+/* cudaError_t of the last failing CUDA call made by this library on the calling thread. */
+int pa_last_cuda_error(void);
+
+/* PA_ABI_VERSION the library was built with. */
+int pa_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PA_DECODE_SM100_H */

@@ -1,0 +1,174 @@
+"""GPU parity of the CUDA operator (through the C ABI) against the oracle and the fixtures."""
+import ctypes as C
+
+import pytest
+import torch
+
+from _util import (ATOL, GOLDEN_CASES, RTOL, assert_close, golden_inputs, load_golden, oracle_output,
+                   run_operator)
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _status():
+    return torch.zeros((), dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("name", sorted(GOLDEN_CASES))
+def test_operator_matches_reference_golden(name):
+    """Same seeded inputs as the fixture (built on CPU, moved to the GPU); the expected output is
+    what the reference's own PyTorch path produced."""
+    gold = load_golden(name)
+    inp = golden_inputs(name).to(DEV)
+    st = _status()
+    out, res = run_operator(inp, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    err = assert_close(out, gold["out"], what=name)
+    # far inside the tolerance in practice: the arithmetic is exact up to fp32 accumulation,
+    # bf16-precision probabilities and the bf16 rounding of the partial outputs
+    assert err < 8e-3, f"{name}: max abs err {err}"
+
+
+@pytest.mark.parametrize("name", ["cfg1_small", "gqa4_ragged", "mtp2_g8", "mtp4_g2_pertoken", "partition512"])
+def test_partition_intermediates(name):
+    """exp_sums / max_logits / tmp_output against the exact-fp32 split-KV statement."""
+    from oracle import pa_oracle
+    cpu = golden_inputs(name)
+    c = cpu.cfg
+    ks, vs = cpu.flat_scales()
+    m_ref, l_ref, o_ref = pa_oracle.split_kv_partials(cpu.query, cpu.key_cache, cpu.value_cache, cpu.block_tables,
+                                                      cpu.context_lens, c.query_len, cpu.softmax_scale,
+                                                      c.partition_size, ks, vs)
+    inp = cpu.to(DEV)
+    _, res = run_operator(inp)
+    torch.cuda.synchronize()
+    m, l, o = res["maximum_logits"].cpu(), res["exponential_sums"].cpu(), res["temporary_output"].float().cpu()
+    for s in range(c.num_seqs):
+        np_s = (int(cpu.context_lens[s]) + c.partition_size - 1) // c.partition_size
+        ms, ls, os_ = m[s, :, :np_s], l[s, :, :np_s], o[s, :, :np_s]
+        mr, lr, orr = m_ref[s, :, :np_s], l_ref[s, :, :np_s], o_ref[s, :, :np_s]
+        live = lr > 0
+        assert torch.equal(torch.isinf(ms), ~live)
+        assert torch.allclose(ms[live], mr[live], atol=1e-4, rtol=1e-5)
+        assert torch.allclose(ls, lr, atol=1e-4, rtol=2e-4)
+        assert torch.allclose(os_, orr, atol=6e-3, rtol=8e-3)
+
+
+def test_workspaces_need_no_clearing_and_runs_are_bit_identical():
+    inp = golden_inputs("gqa4_ragged").to(DEV)
+    c = inp.cfg
+    P = (inp.max_context + c.partition_size - 1) // c.partition_size
+    eqg = c.q_heads // c.kv_heads * c.query_len
+    shape = (c.num_seqs, c.kv_heads, P, eqg)
+    outs = []
+    for fill in (float("nan"), 1e30):
+        es = torch.full(shape, fill, dtype=torch.float32, device=DEV)
+        ml = torch.full(shape, fill, dtype=torch.float32, device=DEV)
+        tmp = torch.full(shape + (c.head_size,), fill, dtype=torch.bfloat16, device=DEV)
+        out, _ = run_operator(inp, exp_sums=es, max_logits=ml, tmp_output=tmp)
+        outs.append(out.clone())
+    torch.cuda.synchronize()
+    assert not torch.isnan(outs[0]).any()
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    assert_close(outs[0], load_golden("gqa4_ragged")["out"], what="poisoned workspaces")
+
+
+def test_garbage_beyond_context_is_ignored():
+    """Bytes of the last page past the context length (NaN patterns included) and block-table
+    entries past the last valid page must not influence the result."""
+    cpu = golden_inputs("cfg1_small")
+    inp = cpu.to(DEV)
+    base, _ = run_operator(inp)
+    bs = cpu.cfg.block_size
+    k = inp.key_cache.clone().view(torch.uint8)
+    v = inp.value_cache.clone().view(torch.uint8)
+    bt = inp.block_tables.clone()
+    for s in range(cpu.cfg.num_seqs):
+        ctx = int(cpu.context_lens[s])
+        nblk = (ctx + bs - 1) // bs
+        last = int(cpu.block_tables[s, nblk - 1])
+        used = ctx - (nblk - 1) * bs
+        if used < bs:
+            k[last, :, :, used:, :] = 0x7F   # e4m3fn NaN
+            v[last, :, :, used:] = 0xFF
+        bt[s, nblk:] = 2 ** 30               # would fault if it were ever dereferenced
+    inp.key_cache = k.view(torch.float8_e4m3fn)
+    inp.value_cache = v.view(torch.float8_e4m3fn)
+    inp.block_tables = bt
+    st = _status()
+    out, _ = run_operator(inp, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert torch.equal(out.view(torch.int16), base.view(torch.int16))
+
+
+def test_bad_page_id_and_long_context_are_clamped_and_reported():
+    from triton_op_b200 import _lib
+    inp = golden_inputs("cfg1_small").to(DEV)
+    inp.block_tables = inp.block_tables.clone()
+    inp.block_tables[0, 0] = 10 ** 6
+    st = _status()
+    run_operator(inp, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) & _lib.PA_DEV_BAD_PAGE_ID
+    inp2 = golden_inputs("cfg1_small").to(DEV)
+    inp2.context_lens = inp2.context_lens.clone()
+    inp2.context_lens[1] = inp2.block_tables.shape[1] * 16 + 5
+    st2 = _status()
+    run_operator(inp2, status=st2)
+    torch.cuda.synchronize()
+    assert int(st2.item()) & _lib.PA_DEV_CTX_TOO_LONG
+
+
+def test_tuning_knobs_do_not_change_results():
+    inp = golden_inputs("gqa4_ragged").to(DEV)
+    base, _ = run_operator(inp)
+    for tune in ({"warps": 4}, {"stages": 2}, {"ctas": 3}, {"warps": 4, "stages": 2, "ctas": 1}):
+        out, _ = run_operator(inp, tune=tune)
+        assert torch.equal(out.view(torch.int16), base.view(torch.int16)), tune
+
+
+def test_zero_length_sequences_and_empty_batch():
+    from triton_op_b200.inputs import DecodeConfig, make_inputs
+    cfg = DecodeConfig("zeros", 5, 8, 2, 16, 1, ("fixed", 100))
+    ctx = torch.tensor([0, 100, 1, 0, 257], dtype=torch.int32)
+    cpu = make_inputs(cfg, seed=3, context_lens=ctx)
+    ref = oracle_output(_nonempty(cpu))
+    out, _ = run_operator(cpu.to(DEV))
+    torch.cuda.synchronize()
+    keep = [1, 2, 4]
+    assert_close(out[keep], ref, what="non-empty sequences")
+    assert torch.count_nonzero(out[[0, 3]].float()) == 0   # empty context -> zeros
+
+
+def _nonempty(inp):
+    """The same workload without its zero-length sequences (the PyTorch path cannot take them)."""
+    import copy
+    keep = [i for i in range(inp.cfg.num_seqs) if int(inp.context_lens[i]) > 0]
+    out = copy.copy(inp)
+    out.cfg = type(inp.cfg)(**{**inp.cfg.__dict__, "num_seqs": len(keep)})
+    out.query_tokens = inp.query_tokens[keep]
+    out.query = inp.query[keep]
+    out.block_tables = inp.block_tables[keep]
+    out.context_lens = inp.context_lens[keep]
+    return out
+
+
+def test_llama8b_shape_full_size_against_oracle_on_device():
+    """The benchmark configuration at full size; the oracle runs on the GPU in fp32."""
+    from triton_op_b200.inputs import CONFIGS, make_inputs
+    inp = make_inputs(CONFIGS["cfg2_llama8b"], seed=0, device=DEV)
+    st = _status()
+    out, res = run_operator(inp, status=st)
+    ref = oracle_output(inp)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert_close(out, ref, what="cfg2_llama8b")
+    # size-independent property: probabilities sum to one, so with V == const the output is const
+    inp.value_cache = torch.full_like(inp.value_cache.float(), 1.5).to(torch.float8_e4m3fn)
+    out1, _ = run_operator(inp)
+    expect = 1.5 * float(inp.value_scale)
+    assert torch.allclose(out1.float(), torch.full_like(out1.float(), expect), rtol=1e-2, atol=0)

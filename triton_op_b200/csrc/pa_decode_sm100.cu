@@ -1,0 +1,352 @@
+// Host side of the C ABI declared in include/pa_decode_sm100.h: argument validation, the
+// shared-memory carve and grid of the partition kernel, and the launches.  Nothing here
+// allocates device memory, synchronises or touches any stream but the caller's.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "../../include/pa_decode_sm100.h"
+#include "pa_partition_fp8.cuh"
+#include "pa_reduce.cuh"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  bool ready = false;
+};
+constexpr int kMaxDevices = 64;
+DeviceInfo g_dev[kMaxDevices];
+
+int cuda_fail(cudaError_t e) {
+  g_last_cuda_error = (int)e;
+  return PA_ERR_CUDA;
+}
+
+// Device attributes are immutable, so a benign race between threads writes the same values.
+int device_info(DeviceInfo** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= kMaxDevices) return PA_ERR_UNSUPPORTED;
+  DeviceInfo& d = g_dev[dev];
+  if (!d.ready) {
+    int sm = 0, smem = 0;
+    e = cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    if (e != cudaSuccess) return cuda_fail(e);
+    d.sm_count = sm;
+    d.max_smem_optin = smem;
+    d.ready = true;
+  }
+  *out = &d;
+  return PA_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int round_up(int v, int a) { return (v + a - 1) / a * a; }
+
+struct LaunchPlan {
+  pa::KernelParams kp;
+  int warps = 0;      // consumer warps per CTA
+  int mtiles = 0;     // 8-row query tiles per warp
+  bool per_token = false;
+  int grid = 0;
+  int smem = 0;
+};
+
+// Validation common to every entry point that reads PaDecodeParams.
+int validate(const PaDecodeParams* p, bool need_partition_inputs, bool need_out) {
+  if (!p) return PA_ERR_NULL_POINTER;
+  if (p->struct_size != sizeof(PaDecodeParams) || p->abi_version != PA_ABI_VERSION) return PA_ERR_ABI;
+  if (p->num_seqs < 0 || p->num_kv_heads <= 0 || p->query_group_size <= 0 || p->query_len <= 0 ||
+      p->block_size <= 0 || p->partition_size <= 0 || p->max_partitions <= 0 ||
+      p->max_blocks_per_seq <= 0 || p->num_blocks <= 0)
+    return PA_ERR_BAD_SHAPE;
+  if (p->head_size != pa::kD) return PA_ERR_UNSUPPORTED;
+  if (p->query_len > 4) return PA_ERR_UNSUPPORTED;  // reference: QUERY_SEQ_LEN <= 4
+  if (p->out_dtype != PA_DT_BF16) return PA_ERR_UNSUPPORTED;
+  if (!p->context_lens || !p->exp_sums || !p->max_logits || !p->tmp_out) return PA_ERR_NULL_POINTER;
+  if (need_out && !p->out) return PA_ERR_NULL_POINTER;
+  if (p->partition_size % p->block_size != 0 && p->block_size % p->partition_size != 0)
+    return PA_ERR_BAD_SHAPE;
+  if (need_partition_inputs) {
+    if (!p->query || !p->key_cache || !p->value_cache || !p->block_tables) return PA_ERR_NULL_POINTER;
+    if (p->kv_quant_mode != PA_QUANT_NONE && (!p->key_scale || !p->value_scale))
+      return PA_ERR_NULL_POINTER;
+    if (p->q_quant_mode != PA_QUANT_NONE && !p->query_scale) return PA_ERR_NULL_POINTER;
+  }
+  if ((p->tmp_stride_row & 7) || (p->tmp_stride_part & 7) || (p->tmp_stride_head & 7) ||
+      (p->tmp_stride_seq & 7) || !aligned16(p->tmp_out))
+    return PA_ERR_ALIGNMENT;
+  if (need_out && ((p->out_stride_head & 3) || (p->out_stride_seq & 3) ||
+                   (reinterpret_cast<uintptr_t>(p->out) & 7u)))
+    return PA_ERR_ALIGNMENT;
+  return PA_OK;
+}
+
+int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
+  int rc = validate(p, true, false);
+  if (rc != PA_OK) return rc;
+  DeviceInfo* dev = nullptr;
+  rc = device_info(&dev);
+  if (rc != PA_OK) return rc;
+
+  const int eqG = p->query_group_size * p->query_len;
+  if (p->kv_dtype != PA_DT_E4M3FN || p->q_dtype != PA_DT_BF16) return PA_ERR_UNSUPPORTED;
+  if (p->block_size != 16) return PA_ERR_UNSUPPORTED;
+  if (p->v_layout != PA_V_NORMAL) return PA_ERR_UNSUPPORTED;
+  if (p->alibi_slopes) return PA_ERR_UNSUPPORTED;
+  if (eqG > 16) return PA_ERR_UNSUPPORTED;
+  if (p->partition_size % pa::kStageTokens != 0 || p->partition_size / p->block_size > 32)
+    return PA_ERR_UNSUPPORTED;
+  // bulk copies: 16-byte aligned sources, contiguous page-of-one-head runs
+  if (!aligned16(p->key_cache) || !aligned16(p->value_cache) || !aligned16(p->query))
+    return PA_ERR_ALIGNMENT;
+  if ((p->k_stride_block & 15) || (p->k_stride_head & 15) || (p->v_stride_block & 15) ||
+      (p->v_stride_head & 15))
+    return PA_ERR_ALIGNMENT;
+  if (p->q_stride_head != pa::kD || (p->q_stride_seq & 7)) return PA_ERR_ALIGNMENT;
+  const bool per_token = p->kv_quant_mode == PA_QUANT_PER_TOKEN;
+  if (per_token) {
+    if (!aligned16(p->key_scale) || !aligned16(p->value_scale) || (p->kv_scale_stride_block & 3) ||
+        (p->kv_scale_stride_head & 3))
+      return PA_ERR_ALIGNMENT;
+  }
+
+  pa::KernelParams& k = plan->kp;
+  memset(&k, 0, sizeof(k));
+  k.q = static_cast<const uint8_t*>(p->query);
+  k.k = static_cast<const uint8_t*>(p->key_cache);
+  k.v = static_cast<const uint8_t*>(p->value_cache);
+  k.block_tables = p->block_tables;
+  k.context_lens = p->context_lens;
+  k.q_scale = p->query_scale;
+  k.k_scale = p->key_scale;
+  k.v_scale = p->value_scale;
+  k.exp_sums = p->exp_sums;
+  k.max_logits = p->max_logits;
+  k.tmp_out = static_cast<uint8_t*>(p->tmp_out);
+  k.status = p->status;
+  k.S = p->num_seqs;
+  k.Hkv = p->num_kv_heads;
+  k.G = p->query_group_size;
+  k.L = p->query_len;
+  k.eqG = eqG;
+  k.block_size = p->block_size;
+  k.num_blocks = p->num_blocks;
+  k.max_blocks_per_seq = p->max_blocks_per_seq;
+  k.partition_size = p->partition_size;
+  k.max_partitions = p->max_partitions;
+  k.pages_per_partition = p->partition_size / p->block_size;
+  const int64_t cap = (int64_t)p->max_blocks_per_seq * p->block_size;
+  k.ctx_cap = cap > 0x7fffffff ? 0x7fffffff : (int32_t)cap;
+  k.q_stride_seq = p->q_stride_seq * 2;    // bf16 -> bytes
+  k.q_stride_head = p->q_stride_head * 2;
+  k.k_stride_block = p->k_stride_block;    // e4m3: elements are bytes
+  k.k_stride_head = p->k_stride_head;
+  k.v_stride_block = p->v_stride_block;
+  k.v_stride_head = p->v_stride_head;
+  k.bt_stride_seq = p->bt_stride_seq;
+  k.q_scale_stride_seq = p->q_scale_stride_seq;
+  k.kvs_stride_block = p->kv_scale_stride_block;
+  k.kvs_stride_head = p->kv_scale_stride_head;
+  k.ws_stride_seq = p->ws_stride_seq;
+  k.ws_stride_head = p->ws_stride_head;
+  k.ws_stride_part = p->ws_stride_part;
+  k.tmp_stride_seq = p->tmp_stride_seq;
+  k.tmp_stride_head = p->tmp_stride_head;
+  k.tmp_stride_part = p->tmp_stride_part;
+  k.tmp_stride_row = p->tmp_stride_row;
+  k.q_quant_mode = p->q_quant_mode;
+  k.kv_quant_mode = p->kv_quant_mode;
+  k.softmax_scale = p->softmax_scale;
+
+  plan->per_token = per_token;
+  plan->mtiles = eqG <= 8 ? 1 : 2;
+  plan->warps = p->tune_warps > 0 ? p->tune_warps : 8;
+  if (plan->warps != 4 && plan->warps != 8) return PA_ERR_UNSUPPORTED;
+
+  // shared-memory carve
+  const int stage = pa::stage_bytes(per_token);
+  const int qbuf = plan->mtiles * 8 * pa::kQRowBytes;
+  int off = pa::kSmemHeadBytes;
+  k.off_seq_offsets = off;
+  off += round_up((p->num_seqs + 1) * 4, 16);
+  k.off_seq_ctx = off;
+  off += round_up(p->num_seqs * 4 + 4, 16);
+  off = round_up(off, 128);
+  k.off_q = off;
+  off += plan->warps * qbuf;
+  off = round_up(off, 128);
+  k.off_ring = off;
+  int stages = (dev->max_smem_optin - off) / (plan->warps * stage);
+  if (stages > pa::kMaxStages) stages = pa::kMaxStages;
+  if (p->tune_stages > 0 && p->tune_stages < stages) stages = p->tune_stages;
+  if (stages < 2) return PA_ERR_TOO_LARGE;  // num_seqs too large for the in-kernel index
+  k.num_stages = stages;
+  plan->smem = off + plan->warps * stages * stage;
+
+  // persistent grid: one CTA per SM, fewer when there cannot be that many work items
+  int64_t parts_cap = (cap + p->partition_size - 1) / p->partition_size;
+  if (parts_cap > p->max_partitions) parts_cap = p->max_partitions;
+  const int64_t items_cap = (int64_t)p->num_seqs * p->num_kv_heads * parts_cap;
+  int64_t grid = (items_cap + plan->warps - 1) / plan->warps;
+  if (grid > dev->sm_count) grid = dev->sm_count;
+  if (p->tune_ctas > 0 && p->tune_ctas < grid) grid = p->tune_ctas;
+  if (grid < 1) grid = 1;
+  plan->grid = (int)grid;
+  return PA_OK;
+}
+
+template <int NW, int MT, bool PT>
+int launch_partition_t(const LaunchPlan& plan, cudaStream_t stream) {
+  auto kern = pa::pa_partition_fp8_p16_kernel<NW, MT, PT>;
+  // Raising the dynamic shared-memory limit is per function and per device; repeating the
+  // call is cheap and keeps the library free of per-device mutable state.
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
+  if (e != cudaSuccess) return cuda_fail(e);
+  kern<<<plan.grid, NW * 32, plan.smem, stream>>>(plan.kp);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return PA_OK;
+}
+
+int launch_partition(const LaunchPlan& plan, cudaStream_t stream) {
+  if (plan.kp.S == 0) return PA_OK;
+#define PA_CASE(NW, MT, PT) \
+  if (plan.warps == NW && plan.mtiles == MT && plan.per_token == PT) return launch_partition_t<NW, MT, PT>(plan, stream);
+  PA_CASE(8, 1, false)
+  PA_CASE(8, 1, true)
+  PA_CASE(8, 2, false)
+  PA_CASE(8, 2, true)
+  PA_CASE(4, 1, false)
+  PA_CASE(4, 1, true)
+  PA_CASE(4, 2, false)
+  PA_CASE(4, 2, true)
+#undef PA_CASE
+  return PA_ERR_UNSUPPORTED;
+}
+
+int launch_reduce(const PaDecodeParams* p, float* tri_m, float* tri_l, float* tri_o,
+                  cudaStream_t stream) {
+  pa::ReduceParams r;
+  memset(&r, 0, sizeof(r));
+  r.out = static_cast<uint8_t*>(p->out);
+  r.exp_sums = p->exp_sums;
+  r.max_logits = p->max_logits;
+  r.tmp_out = static_cast<const uint8_t*>(p->tmp_out);
+  r.context_lens = p->context_lens;
+  r.tri_m = tri_m;
+  r.tri_l = tri_l;
+  r.tri_o = tri_o;
+  r.S = p->num_seqs;
+  r.Hkv = p->num_kv_heads;
+  r.eqG = p->query_group_size * p->query_len;
+  r.partition_size = p->partition_size;
+  r.max_partitions = p->max_partitions;
+  const int64_t cap = (int64_t)p->max_blocks_per_seq * p->block_size;
+  r.ctx_cap = cap > 0x7fffffff ? 0x7fffffff : (int32_t)cap;
+  r.out_stride_seq = p->out_stride_seq;
+  r.out_stride_head = p->out_stride_head;
+  r.ws_stride_seq = p->ws_stride_seq;
+  r.ws_stride_head = p->ws_stride_head;
+  r.ws_stride_part = p->ws_stride_part;
+  r.tmp_stride_seq = p->tmp_stride_seq;
+  r.tmp_stride_head = p->tmp_stride_head;
+  r.tmp_stride_part = p->tmp_stride_part;
+  r.tmp_stride_row = p->tmp_stride_row;
+  const int64_t rows = (int64_t)r.S * r.Hkv * r.eqG;
+  if (rows == 0) return PA_OK;
+  const int64_t blocks = (rows + 3) / 4;
+  if (blocks > 0x7fffffff) return PA_ERR_TOO_LARGE;
+  pa::pa_reduce_kernel<<<(unsigned)blocks, 128, 0, stream>>>(r);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return PA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int pa_partition_sm100(const PaDecodeParams* params, void* stream) {
+  LaunchPlan plan;
+  int rc = make_plan(params, &plan);
+  if (rc != PA_OK) return rc;
+  return launch_partition(plan, static_cast<cudaStream_t>(stream));
+}
+
+int pa_reduce_sm100(const PaDecodeParams* params, float* tri_m, float* tri_l, float* tri_o,
+                    void* stream) {
+  const bool triples = tri_m || tri_l || tri_o;
+  if (triples && !(tri_m && tri_l && tri_o)) return PA_ERR_NULL_POINTER;
+  int rc = validate(params, false, !triples);
+  if (rc != PA_OK) return rc;
+  if (triples && (!aligned16(tri_o))) return PA_ERR_ALIGNMENT;
+  return launch_reduce(params, tri_m, tri_l, tri_o, static_cast<cudaStream_t>(stream));
+}
+
+int pa_decode_sm100(const PaDecodeParams* params, void* stream) {
+  LaunchPlan plan;
+  int rc = make_plan(params, &plan);
+  if (rc != PA_OK) return rc;
+  rc = validate(params, true, true);
+  if (rc != PA_OK) return rc;
+  rc = launch_partition(plan, static_cast<cudaStream_t>(stream));
+  if (rc != PA_OK) return rc;
+  return launch_reduce(params, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int pa_merge_triples_sm100(void* out, int64_t out_stride_row, const float* m, const float* l,
+                           const float* o, int32_t num_shards, int32_t num_rows, int32_t head_size,
+                           void* stream) {
+  if (!out || !m || !l || !o) return PA_ERR_NULL_POINTER;
+  if (num_shards <= 0 || num_rows < 0) return PA_ERR_BAD_SHAPE;
+  if (head_size != pa::kD) return PA_ERR_UNSUPPORTED;
+  if (!aligned16(o) || (reinterpret_cast<uintptr_t>(out) & 7u) || (out_stride_row & 3))
+    return PA_ERR_ALIGNMENT;
+  if (num_rows == 0) return PA_OK;
+  const int blocks = (num_rows + 3) / 4;
+  pa::pa_merge_triples_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint8_t*>(out), out_stride_row, m, l, o, num_shards, num_rows);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return PA_OK;
+}
+
+int pa_query_launch_sm100(const PaDecodeParams* params, int32_t* grid_ctas, int32_t* cta_threads,
+                          int32_t* smem_bytes, int32_t* ring_stages) {
+  LaunchPlan plan;
+  int rc = make_plan(params, &plan);
+  if (rc != PA_OK) return rc;
+  if (grid_ctas) *grid_ctas = plan.grid;
+  if (cta_threads) *cta_threads = plan.warps * 32;
+  if (smem_bytes) *smem_bytes = plan.smem;
+  if (ring_stages) *ring_stages = plan.kp.num_stages;
+  return PA_OK;
+}
+
+const char* pa_strerror(int status) {
+  switch (status) {
+    case PA_OK: return "ok";
+    case PA_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case PA_ERR_BAD_SHAPE: return "a size is zero, negative or inconsistent";
+    case PA_ERR_UNSUPPORTED: return "shape, dtype or layout not supported by the sm_100a kernels";
+    case PA_ERR_ALIGNMENT: return "a pointer or stride is not aligned as the bulk copies require";
+    case PA_ERR_CUDA: return "a CUDA runtime call failed (see pa_last_cuda_error)";
+    case PA_ERR_ABI: return "PaDecodeParams.struct_size / abi_version do not match this library";
+    case PA_ERR_TOO_LARGE: return "a size exceeds a fixed limit of the library";
+    default: return "unknown status";
+  }
+}
+
+int pa_last_cuda_error(void) { return g_last_cuda_error; }
+
+int pa_abi_version(void) { return PA_ABI_VERSION; }
+
+}  // extern "C"

@@ -1,0 +1,137 @@
+// Cross-partition log-sum-exp reduce and the cross-shard triple merge.
+//
+// pa_reduce_kernel restates paged_attention_decode_v2_reduce_kernel
+// (pa_decode_triton_gluon_fp8.py:1187-1333 in yanguahe/triton_op):
+//   np = ceil(ctx / partition_size); M = max_p m_p; w_p = l_p * exp(m_p - M);
+//   out = sum_p (w_p / sum w) * o_p   (fp32 accumulate, bf16 store).
+// Differences by design: it loops over the partitions with a running sum instead of loading a
+// [P_pow2, eqG, D] tile at once, so the partition count is unbounded; a partition whose l is 0
+// (every key masked for that row) gets weight 0 instead of relying on zero-filled workspaces.
+#pragma once
+
+#include "pa_common.cuh"
+#include "pa_params.cuh"
+
+namespace pa {
+
+struct ReduceParams {
+  uint8_t* out;                 // bf16 [S, Hkv*eqG, D]; may be null when triples are stored
+  const float* exp_sums;
+  const float* max_logits;
+  const uint8_t* tmp_out;       // bf16
+  const int32_t* context_lens;
+  float* tri_m;                 // optional fp32 triples
+  float* tri_l;
+  float* tri_o;
+  int32_t S, Hkv, eqG, partition_size, max_partitions, ctx_cap;
+  int64_t out_stride_seq, out_stride_head;
+  int64_t ws_stride_seq, ws_stride_head, ws_stride_part;
+  int64_t tmp_stride_seq, tmp_stride_head, tmp_stride_part, tmp_stride_row;
+};
+
+// One warp per output row (sequence, kv head, row r); lane owns head dims 4*lane..4*lane+3.
+__global__ void __launch_bounds__(128) pa_reduce_kernel(const __grid_constant__ ReduceParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t n_rows = (int64_t)p.S * p.Hkv * p.eqG;
+  if (row >= n_rows) return;
+  const int r = (int)(row % p.eqG);
+  const int head = (int)((row / p.eqG) % p.Hkv);
+  const int seq = (int)(row / ((int64_t)p.eqG * p.Hkv));
+
+  int ctx = p.context_lens[seq];
+  ctx = max(0, min(ctx, p.ctx_cap));
+  int np = (ctx + p.partition_size - 1) / p.partition_size;
+  np = min(np, p.max_partitions);
+
+  const int64_t ws_base = (int64_t)seq * p.ws_stride_seq + (int64_t)head * p.ws_stride_head + r;
+  const int64_t tmp_base = (int64_t)seq * p.tmp_stride_seq + (int64_t)head * p.tmp_stride_head +
+                           (int64_t)r * p.tmp_stride_row + 4 * lane;
+
+  float M = -INFINITY;
+  for (int i = lane; i < np; i += 32) M = fmaxf(M, p.max_logits[ws_base + (int64_t)i * p.ws_stride_part]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(kFullMask, M, o));
+
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float W = 0.f;
+  for (int p0 = 0; p0 < np; p0 += 32) {
+    const int pi = p0 + lane;
+    float w = 0.f;
+    if (pi < np) {
+      const float m = p.max_logits[ws_base + (int64_t)pi * p.ws_stride_part];
+      const float l = p.exp_sums[ws_base + (int64_t)pi * p.ws_stride_part];
+      if (l > 0.f && m > -INFINITY) w = l * expf(m - M);
+    }
+    const int cnt = min(32, np - p0);
+#pragma unroll 4
+    for (int j = 0; j < cnt; ++j) {
+      const float wj = __shfl_sync(kFullMask, w, j);
+      const uint2 raw = *reinterpret_cast<const uint2*>(
+          p.tmp_out + 2 * (tmp_base + (int64_t)(p0 + j) * p.tmp_stride_part));
+      W += wj;
+      if (wj != 0.f) {  // a zero-weight partition may hold anything
+        acc[0] = fmaf(wj, bf16_lo_to_f32(raw.x), acc[0]);
+        acc[1] = fmaf(wj, bf16_hi_to_f32(raw.x), acc[1]);
+        acc[2] = fmaf(wj, bf16_lo_to_f32(raw.y), acc[2]);
+        acc[3] = fmaf(wj, bf16_hi_to_f32(raw.y), acc[3]);
+      }
+    }
+  }
+  const float inv = W > 0.f ? 1.0f / W : 0.f;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) acc[e] *= inv;
+
+  if (p.out) {
+    uint2 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    *reinterpret_cast<uint2*>(p.out + 2 * ((int64_t)seq * p.out_stride_seq +
+                                           ((int64_t)head * p.eqG + r) * p.out_stride_head + 4 * lane)) = o;
+  }
+  if (p.tri_o) {
+    if (lane == 0) {
+      p.tri_m[row] = M;
+      p.tri_l[row] = W;
+    }
+    *reinterpret_cast<float4*>(p.tri_o + row * kD + 4 * lane) =
+        make_float4(acc[0], acc[1], acc[2], acc[3]);
+  }
+}
+
+// One warp per row; merges `num_shards` (m, l, o) triples.
+__global__ void __launch_bounds__(128)
+pa_merge_triples_kernel(uint8_t* out, int64_t out_stride_row, const float* __restrict__ m,
+                        const float* __restrict__ l, const float* __restrict__ o, int num_shards,
+                        int num_rows) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= num_rows) return;
+  float M = -INFINITY;
+  for (int s = 0; s < num_shards; ++s) {
+    const float ls = l[(int64_t)s * num_rows + row];
+    const float ms = m[(int64_t)s * num_rows + row];
+    if (ls > 0.f) M = fmaxf(M, ms);
+  }
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float W = 0.f;
+  for (int s = 0; s < num_shards; ++s) {
+    const float ls = l[(int64_t)s * num_rows + row];
+    const float ms = m[(int64_t)s * num_rows + row];
+    if (!(ls > 0.f) || !(ms > -INFINITY)) continue;
+    const float w = ls * expf(ms - M);
+    const float4 v = *reinterpret_cast<const float4*>(o + ((int64_t)s * num_rows + row) * kD + 4 * lane);
+    W += w;
+    acc[0] = fmaf(w, v.x, acc[0]);
+    acc[1] = fmaf(w, v.y, acc[1]);
+    acc[2] = fmaf(w, v.z, acc[2]);
+    acc[3] = fmaf(w, v.w, acc[3]);
+  }
+  const float inv = W > 0.f ? 1.0f / W : 0.f;
+  uint2 res;
+  res.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
+  res.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
+  *reinterpret_cast<uint2*>(out + 2 * (row * out_stride_row + 4 * lane)) = res;
+}
+
+}  // namespace pa
