@@ -62,6 +62,9 @@ typedef enum PaVLayout {
 #define PA_DEV_BAD_PAGE_ID    2  /* a block-table entry was outside [0, num_blocks); it was clamped */
 #define PA_DEV_CTX_TOO_LONG   4  /* a context length exceeded max_blocks_per_seq*block_size; it was clamped */
 
+/* Size, in uint64 words, of the optional trace buffer: [8 roles][item < 64][4 points]. */
+#define PA_TRACE_WORDS (8 * 64 * 4)
+
 /*
  * One decode call.  Symbols: S num_seqs, Hkv num_kv_heads, G query heads per kv head,
  * L query_len (MTP), eqG = L*G, D head_size (128), bs block_size, P max_partitions,
@@ -93,6 +96,8 @@ typedef struct PaDecodeParams {
   float* max_logits;           /* [S, Hkv, P, eqG] fp32 */
   void* tmp_out;               /* [S, Hkv, P, eqG, D] out_dtype, already divided by exp_sums */
   int32_t* status;             /* optional device int32, OR-ed with PA_DEV_* bits */
+  uint64_t* trace;             /* optional tuning aid: device buffer of PA_TRACE_WORDS uint64 that
+                                * receives SM-clock stamps of CTA 0's pipeline roles; NULL normally */
 
   /* sizes */
   int32_t num_seqs;            /* S */

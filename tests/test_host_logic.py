@@ -42,7 +42,7 @@ def test_struct_mirror_matches_header_field_order():
         decl = decl.strip()
         if not decl:
             continue
-        decl = re.sub(r"^(const\s+)?(void|float|int32_t|uint32_t|int64_t)\s*\*?\s*", "", decl)
+        decl = re.sub(r"^(const\s+)?(void|float|int32_t|uint32_t|int64_t|uint64_t)\s*\*?\s*", "", decl)
         names += [n.strip().lstrip("*") for n in decl.split(",")]
     assert names == [f[0] for f in _lib.PaDecodeParams._fields_]
 

@@ -17,6 +17,7 @@ PA_DT_BF16, PA_DT_E4M3FN = 0, 1
 PA_QUANT_NONE, PA_QUANT_PER_TENSOR, PA_QUANT_PER_TOKEN = -1, 0, 1
 PA_V_NORMAL, PA_V_TRANSPOSED = 0, 1
 PA_DEV_WAIT_TIMEOUT, PA_DEV_BAD_PAGE_ID, PA_DEV_CTX_TOO_LONG = 1, 2, 4
+PA_TRACE_WORDS = 8 * 64 * 4
 
 EXPORTS = (
     "pa_decode_sm100", "pa_partition_sm100", "pa_reduce_sm100", "pa_merge_triples_sm100",
@@ -31,7 +32,7 @@ class PaDecodeParams(C.Structure):
         + [(n, C.c_void_p) for n in (
             "out", "query", "key_cache", "value_cache", "block_tables", "context_lens",
             "query_scale", "key_scale", "value_scale", "alibi_slopes",
-            "exp_sums", "max_logits", "tmp_out", "status")]
+            "exp_sums", "max_logits", "tmp_out", "status", "trace")]
         + [(n, C.c_int32) for n in (
             "num_seqs", "num_kv_heads", "query_group_size", "query_len", "head_size",
             "block_size", "num_blocks", "max_blocks_per_seq", "partition_size", "max_partitions")]

@@ -15,11 +15,13 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr unsigned kFullMask = 0xffffffffu;
 
-// Upper bound on polls of one mbarrier phase.  Each failed poll already blocks inside
-// try_wait for a hardware-defined slice and then sleeps, so the limit is of the order of a
-// second; a healthy copy completes in microseconds.  When it runs out the warp records
+// Upper bound on polls of one mbarrier phase.  The first kSpinPolls polls go back to back (a
+// sleeping waiter would add its wake-up latency to every hand-off of the pipeline); after that
+// the waiter sleeps between polls, so the limit is of the order of a second while a healthy
+// copy completes in microseconds.  When the limit runs out the warp records
 // PA_DEV_WAIT_TIMEOUT and stops issuing work, so a lost copy can never spin a GPU forever.
-constexpr uint32_t kWaitPollLimit = 1u << 21;
+constexpr uint32_t kSpinPolls = 1u << 15;
+constexpr uint32_t kWaitPollLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -60,7 +62,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   for (uint32_t it = 0; it < kWaitPollLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 32) __nanosleep(it > 4096 ? 256 : 32);
+    if (it > kSpinPolls) __nanosleep(200);
   }
   return false;
 }

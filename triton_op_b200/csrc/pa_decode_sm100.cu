@@ -7,6 +7,7 @@
 
 #include "../../include/pa_decode_sm100.h"
 #include "pa_partition_fp8.cuh"
+#include "pa_partition_tc.cuh"
 #include "pa_reduce.cuh"
 
 namespace {
@@ -55,6 +56,7 @@ struct LaunchPlan {
   int warps = 0;      // consumer warps per CTA
   int mtiles = 0;     // 8-row query tiles per warp
   bool per_token = false;
+  bool tensor_path = false;  // tcgen05 kernel (else the mma.sync kernel)
   int grid = 0;
   int smem = 0;
 };
@@ -132,6 +134,7 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   k.max_logits = p->max_logits;
   k.tmp_out = static_cast<uint8_t*>(p->tmp_out);
   k.status = p->status;
+  k.trace = reinterpret_cast<unsigned long long*>(p->trace);
   k.S = p->num_seqs;
   k.Hkv = p->num_kv_heads;
   k.G = p->query_group_size;
@@ -168,6 +171,41 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
 
   plan->per_token = per_token;
   plan->mtiles = eqG <= 8 ? 1 : 2;
+
+  // upper bound on work items, for the grid
+  int64_t parts_cap = (cap + p->partition_size - 1) / p->partition_size;
+  if (parts_cap > p->max_partitions) parts_cap = p->max_partitions;
+  const int64_t items_cap = (int64_t)p->num_seqs * p->num_kv_heads * parts_cap;
+  const int index_bytes = round_up((p->num_seqs + 1) * 4, 16) + round_up(p->num_seqs * 4 + 4, 16);
+
+  // tcgen05 kernel: 256-token partitions, up to 8 query rows per kv head.  tune_warps == 4 / 8
+  // explicitly asks for the mma.sync kernel (kept for the shapes the tensor path does not cover).
+  plan->tensor_path = p->partition_size == pa::tc::kItemTokens && eqG <= 8 && p->tune_warps == 0;
+  if (plan->tensor_path) {
+    plan->warps = pa::tc::kThreads / 32;
+    int off = pa::tc::kHeadBytes;
+    k.off_seq_offsets = off;
+    k.off_seq_ctx = off + round_up((p->num_seqs + 1) * 4, 16);
+    off = round_up(off + index_bytes, 128);
+    k.off_q = off;
+    int slots = pa::tc::kMaxSlots;
+    if (p->tune_stages > 0 && p->tune_stages < slots) slots = p->tune_stages;
+    for (; slots >= 2; --slots) {
+      const int ring = round_up(off + slots * pa::tc::kQSlotBytes + 2 * pa::tc::kPTileBytes, 1024);
+      if (ring + slots * pa::tc::kSlotBytes <= dev->max_smem_optin) {
+        k.off_ring = ring;
+        break;
+      }
+    }
+    if (slots < 2) return PA_ERR_TOO_LARGE;  // num_seqs too large for the in-kernel index
+    k.num_stages = slots;
+    plan->smem = k.off_ring + slots * pa::tc::kSlotBytes;
+    int64_t grid = items_cap < dev->sm_count ? items_cap : dev->sm_count;
+    if (p->tune_ctas > 0 && p->tune_ctas < grid) grid = p->tune_ctas;
+    plan->grid = grid < 1 ? 1 : (int)grid;
+    return PA_OK;
+  }
+
   plan->warps = p->tune_warps > 0 ? p->tune_warps : 8;
   if (plan->warps != 4 && plan->warps != 8) return PA_ERR_UNSUPPORTED;
 
@@ -192,9 +230,6 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   plan->smem = off + plan->warps * stages * stage;
 
   // persistent grid: one CTA per SM, fewer when there cannot be that many work items
-  int64_t parts_cap = (cap + p->partition_size - 1) / p->partition_size;
-  if (parts_cap > p->max_partitions) parts_cap = p->max_partitions;
-  const int64_t items_cap = (int64_t)p->num_seqs * p->num_kv_heads * parts_cap;
   int64_t grid = (items_cap + plan->warps - 1) / plan->warps;
   if (grid > dev->sm_count) grid = dev->sm_count;
   if (p->tune_ctas > 0 && p->tune_ctas < grid) grid = p->tune_ctas;
@@ -216,8 +251,21 @@ int launch_partition_t(const LaunchPlan& plan, cudaStream_t stream) {
   return PA_OK;
 }
 
+template <bool PT>
+int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
+  auto kern = pa::tc::pa_partition_fp8_tc_kernel<PT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
+  if (e != cudaSuccess) return cuda_fail(e);
+  kern<<<plan.grid, pa::tc::kThreads, plan.smem, stream>>>(plan.kp);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return PA_OK;
+}
+
 int launch_partition(const LaunchPlan& plan, cudaStream_t stream) {
   if (plan.kp.S == 0) return PA_OK;
+  if (plan.tensor_path)
+    return plan.per_token ? launch_tensor_t<true>(plan, stream) : launch_tensor_t<false>(plan, stream);
 #define PA_CASE(NW, MT, PT) \
   if (plan.warps == NW && plan.mtiles == MT && plan.per_token == PT) return launch_partition_t<NW, MT, PT>(plan, stream);
   PA_CASE(8, 1, false)

@@ -22,6 +22,7 @@ struct KernelParams {
   float* max_logits;
   uint8_t* tmp_out;            // bf16
   int32_t* status;             // may be null
+  unsigned long long* trace;   // tuning aid: per-role clock stamps of CTA 0; null in normal operation
 
   // sizes
   int32_t S, Hkv, G, L, eqG;

@@ -242,6 +242,7 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
     p.alibi_slopes = alibi_slopes.data_ptr() if alibi_slopes is not None else None
     p.exp_sums, p.max_logits, p.tmp_out = exp_sums.data_ptr(), max_logits.data_ptr(), tmp_output.data_ptr()
     p.status = status.data_ptr() if status is not None else None
+    p.trace = tune["trace"].data_ptr() if tune and tune.get("trace") is not None else None
     p.num_seqs, p.num_kv_heads, p.query_group_size = num_seqs, num_kv_heads, group
     p.query_len, p.head_size, p.block_size = query_sequence_length, head_size, kv_block_size
     p.num_blocks, p.max_blocks_per_seq = num_blocks, block_tables.shape[1]
