@@ -190,9 +190,12 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
     k.off_q = off;
     int slots = pa::tc::kMaxSlots;
     if (p->tune_stages > 0 && p->tune_stages < slots) slots = p->tune_stages;
+    const int qslot = pa::tc::q_slot_bytes(per_token);
     for (; slots >= 2; --slots) {
-      const int ring = round_up(off + slots * pa::tc::kQSlotBytes + 2 * pa::tc::kPTileBytes, 1024);
+      const int off_p = round_up(off + slots * qslot, 128);
+      const int ring = round_up(off_p + pa::tc::kNG * pa::tc::kPTileBytes, 1024);
       if (ring + slots * pa::tc::kSlotBytes <= dev->max_smem_optin) {
+        k.off_p = off_p;
         k.off_ring = ring;
         break;
       }
@@ -251,9 +254,9 @@ int launch_partition_t(const LaunchPlan& plan, cudaStream_t stream) {
   return PA_OK;
 }
 
-template <bool PT>
+template <bool PT, bool TRACE>
 int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
-  auto kern = pa::tc::pa_partition_fp8_tc_kernel<PT>;
+  auto kern = pa::tc::pa_partition_fp8_tc_kernel<PT, TRACE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
   if (e != cudaSuccess) return cuda_fail(e);
   kern<<<plan.grid, pa::tc::kThreads, plan.smem, stream>>>(plan.kp);
@@ -264,8 +267,11 @@ int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
 
 int launch_partition(const LaunchPlan& plan, cudaStream_t stream) {
   if (plan.kp.S == 0) return PA_OK;
-  if (plan.tensor_path)
-    return plan.per_token ? launch_tensor_t<true>(plan, stream) : launch_tensor_t<false>(plan, stream);
+  if (plan.tensor_path) {
+    if (plan.kp.trace != nullptr)  // tuning build of the kernel with the clock stamps compiled in
+      return plan.per_token ? launch_tensor_t<true, true>(plan, stream) : launch_tensor_t<false, true>(plan, stream);
+    return plan.per_token ? launch_tensor_t<true, false>(plan, stream) : launch_tensor_t<false, false>(plan, stream);
+  }
 #define PA_CASE(NW, MT, PT) \
   if (plan.warps == NW && plan.mtiles == MT && plan.per_token == PT) return launch_partition_t<NW, MT, PT>(plan, stream);
   PA_CASE(8, 1, false)

@@ -48,7 +48,8 @@ struct KernelParams {
   int32_t num_stages;          // ring depth per warp
   int32_t off_seq_offsets;     // int32[S+1]: exclusive prefix sum of partitions per sequence
   int32_t off_seq_ctx;         // int32[S]: clamped context lengths
-  int32_t off_q;               // per-warp query staging
+  int32_t off_q;               // query staging (ring of tiles)
+  int32_t off_p;               // probability tiles (tcgen05 kernel)
   int32_t off_ring;            // per-warp stage ring
 };
 

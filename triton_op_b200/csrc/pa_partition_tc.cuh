@@ -27,18 +27,18 @@
 //   V page [D][16 tok]: rows = head dims (128 B between groups of 8), the two K units of an
 //     instruction are two consecutive pages (2048 B apart).
 //
-// One CTA per SM, persistent over work items (an item = one partition of one kv head), twelve
-// warps with fixed roles joined by mbarriers:
-//   warps 0-3, 4-7  two softmax + epilogue groups; a thread = one TMEM lane (a token of S^T, a
-//                   head dim of O^T).  Group g takes the CTA's items g, g+2, ... and owns TMEM
-//                   buffer g, so the per-item latency chain of one group (TMEM loads, reductions,
-//                   P^T stores) overlaps the other group's.
-//   warp  8         tcgen05.mma issue (one lane) and TMEM allocation
-//   warp  9 / 10    K / V producers: one 2 KB bulk copy per page, page ids prefetched an item ahead
-//   warp  11        query producer: bf16 -> hi/lo e4m3 tile in the B-operand layout, per-token scales
+// One CTA per SM, persistent over work items (an item = one partition of one kv head), 4*NG + 4
+// warps with fixed roles joined by mbarriers (NG = 3):
+//   warps 0 .. 4*NG-1   NG softmax + epilogue groups of four warps; a thread = one TMEM lane (a
+//                       token of S^T, a head dim of O^T).  Group g takes the CTA's items g, g+NG,
+//                       ... and owns its own S^T / O^T columns and P^T tile, so the per-item
+//                       latency chain of a group (TMEM loads, reductions, P^T stores) overlaps
+//                       the chains of the other groups.
+//   warp 4*NG           tcgen05.mma issue (one elected lane) and TMEM allocation
+//   warp 4*NG+1 / +2    K / V producers: one 2 KB bulk copy per page, page ids prefetched an item ahead
+//   warp 4*NG+3         query producer: bf16 -> hi/lo e4m3 tile in the B-operand layout, per-token scales
 // A ring of item slots (K 32 KB + V 32 KB each) keeps two items of copies in flight while a
-// third is being consumed; S^T and O^T are double buffered in TMEM so QK^T of item i+1 overlaps
-// the softmax of item i.  Every wait is bounded and reports PA_DEV_WAIT_TIMEOUT.
+// third is being consumed.  Every wait is bounded and reports PA_DEV_WAIT_TIMEOUT.
 #pragma once
 
 #include "pa_common.cuh"
@@ -56,31 +56,52 @@ constexpr int kHalfSlot = kItemPages * kPageBytes;  // 32 KB: K (or V) of one it
 constexpr int kSlotBytes = 2 * kHalfSlot;
 constexpr int kNQ = 16;                             // MMA N: 8 query rows x {hi, lo}
 constexpr int kQTileBytes = kNQ * kD;               // 2 KB: [2 row blocks][8 chunks][8 rows][16 B]
-constexpr int kAuxFloats = 16 + 2 * kItemTokens;    // query pre-scales | k scales | v scales
-constexpr int kQSlotBytes = kQTileBytes + kAuxFloats * 4;  // 4160, a multiple of 64
-constexpr int kPTileBytes = 8 * 512;                // 8 k-steps x [2 row blocks][2 K units][8 rows][16 B]
-constexpr int kTmemCols = 128;                      // S: 2 buffers x 32 columns; O: 2 x 16 at column 64
-constexpr int kThreads = 384;
-constexpr int kWarpMma = 8, kWarpK = 9, kWarpV = 10, kWarpQ = 11;
+constexpr int kNG = 3;                              // softmax groups
+constexpr int kMaxGroups = 4;
+constexpr int kThreads = (4 * kNG + 4) * 32;
 constexpr int kMaxSlots = 4;
+// Query slot: the tile, 16 floats of per-row scales, and (per-token mode) 2 x 256 token scales.
+__host__ __device__ constexpr int q_slot_bytes(bool per_token) {
+  return kQTileBytes + 64 + (per_token ? 2 * kItemTokens * 4 : 0);
+}
+// P^T tile of one item: 8 k-steps x [2 row blocks (hi | lo)][2 K units][8 rows][16 tokens].  The
+// strides are padded off the 128-byte grid so that the byte stores of a warp, which go to four
+// different pages (= K units), fall into different banks.
+constexpr int kPLbo = 144;                          // between the two K units of a k-step
+constexpr int kPSbo = 288;                          // between the hi and the lo row block
+constexpr int kPStep = 560;                         // between k-steps
+constexpr int kPTileBytes = 8 * kPStep;
+// TMEM columns: S^T of group g at 32*g (two 16-column halves), O^T of group g, parity b at
+// 32*kMaxGroups + 32*g + 16*b.
+constexpr int kTmemCols = 256;
+constexpr int kTmemO = 32 * kMaxGroups;
 
 // barrier indices inside the barrier block
+// A parity wait is only meaningful while the waiter is at most one phase ahead of the barrier,
+// so every barrier below is waited on either by one role in item order, or by a role that has
+// first observed an event implying the previous phase (noted at the wait).
 enum : int {
-  kBarKFull = 0, kBarKEmpty = 4, kBarVFull = 8, kBarVEmpty = 12, kBarQFull = 16, kBarQEmpty = 20,
-  kBarSFull = 24, kBarPFull = 26, kBarOFull = 28, kBarOEmpty = 30, kNumBars = 32
+  kBarKQFull = 0,   // [slot] K pages landed (transaction bytes) + query tile written: 2 arrivals
+  kBarVFull = 4,    // [slot] V pages landed
+  kBarQEmpty = 8,   // [slot] the softmax group has read the slot's scales: 4 arrivals
+  kBarSFull = 12,   // [group] QK^T of the group's current item is complete (commit); this also
+                    //         frees the item's K pages and query tile
+  kBarPFull = 16,   // [group] P^T stored, V cleared where needed, S^T consumed: 4 arrivals
+  kBarOFull = 20,   // [group][parity] P.V complete (commit); this also frees the item's V pages
+  kNumBars = 28
 };
-// fixed head of the shared-memory carve (bytes)
-constexpr int kOffBars = 0;                       // 32 mbarriers
-constexpr int kOffTmemPtr = 256;
-constexpr int kOffScan = 272;                     // 32 ints
-// A softmax group keeps two items in flight (softmax of item i+2 runs before the epilogue of
-// item i), so what the epilogue reads is double buffered by the item's parity inside the group.
-constexpr int kOffRedMax = 512;                   // [2 groups][8 q][4 warps] floats
-constexpr int kOffRedSum = 768;                   // [2 groups][2 parities][8 q][4 warps] floats
-constexpr int kOffMFin = 1280;                    // [2 groups][2 parities][8] floats (max, log2 domain)
-constexpr int kOffVMax = 1408;                    // [2 groups][4 warps] floats (per-token V scale max)
-constexpr int kOffVNorm = 1440;                   // [2 groups][2 parities] floats
-constexpr int kHeadBytes = 1536;
+// fixed head of the shared-memory carve (bytes).  A softmax group keeps two items in flight (the
+// softmax of its next item runs before the epilogue of the previous one), so what the epilogue
+// reads is double buffered by the item's parity inside the group.
+constexpr int kOffBars = 0;
+constexpr int kOffTmemPtr = 384;
+constexpr int kOffScan = 400;                     // 32 ints
+constexpr int kOffRedMax = 640;                   // [groups][8 q][4 warps] floats
+constexpr int kOffRedSum = 1152;                  // [groups][2 parities][8 q][4 warps] floats
+constexpr int kOffMFin = 2176;                    // [groups][2 parities][8] floats (max, log2 domain)
+constexpr int kOffVMax = 2432;                    // [groups][4 warps] floats (per-token V scale max)
+constexpr int kOffVNorm = 2496;                   // [groups][2 parities] floats
+constexpr int kHeadBytes = 2560;
 
 // Walks the work items of one role: item k = first, first + step, ...  Decoding an item index
 // into (sequence, partition, head) needs a search in the partition prefix sum; the cursor does
@@ -157,9 +178,13 @@ __device__ __forceinline__ float warp_reduce8(const float (&v)[8], int lane) {
   return c;
 }
 
-template <bool PER_TOKEN>
+// PER_TOKEN: per-token-per-head K/V scales.  TRACE: compile the clock stamps in (tuning builds).
+template <bool PER_TOKEN, bool TRACE>
 __global__ void __launch_bounds__(kThreads, 1)
 pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
+  constexpr int NG = kNG;
+  constexpr int kWarpMma = 4 * NG, kWarpK = 4 * NG + 1, kWarpV = 4 * NG + 2, kWarpQ = 4 * NG + 3;
+  constexpr int kQSlotBytes = q_slot_bytes(PER_TOKEN);
   extern __shared__ __align__(1024) uint8_t smem[];
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -177,23 +202,19 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
   float* v_max = reinterpret_cast<float*>(smem + kOffVMax);
   float* v_norm = reinterpret_cast<float*>(smem + kOffVNorm);
   const uint32_t q_ring = sbase + p.off_q;             // NS x kQSlotBytes
-  const uint32_t p_tiles = q_ring + NS * kQSlotBytes;  // 2 x kPTileBytes (the host carves them here)
+  const uint32_t p_tiles = sbase + p.off_p;            // NG x kPTileBytes
   const uint32_t kv_ring = sbase + p.off_ring;         // NS x kSlotBytes
 
   if (tid == 0) {
     for (int s = 0; s < kMaxSlots; ++s) {
-      mbar_init(bar(kBarKFull, s), 1);
-      mbar_init(bar(kBarKEmpty, s), 1);
+      mbar_init(bar(kBarKQFull, s), 2);
       mbar_init(bar(kBarVFull, s), 1);
-      mbar_init(bar(kBarVEmpty, s), 1);
-      mbar_init(bar(kBarQFull, s), 1);
-      mbar_init(bar(kBarQEmpty, s), 1 + 4);  // QK^T done (commit) + the four warps of a softmax group
+      mbar_init(bar(kBarQEmpty, s), 4);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(bar(kBarSFull, b), 1);
-      mbar_init(bar(kBarPFull, b), 4);
-      mbar_init(bar(kBarOFull, b), 1);
-      mbar_init(bar(kBarOEmpty, b), 4);
+    for (int g = 0; g < kMaxGroups; ++g) {
+      mbar_init(bar(kBarSFull, g), 1);
+      mbar_init(bar(kBarPFull, g), 4);
+      for (int b = 0; b < 2; ++b) mbar_init(bar(kBarOFull, 2 * g + b), 1);
     }
     mbar_fence_init();
     fence_proxy_async();
@@ -204,8 +225,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + kOffTmemPtr);
-  const uint32_t tmem_s = tmem_base;        // S^T buffer b at column 32*b (+16 for tg = 1)
-  const uint32_t tmem_o = tmem_base + 64;   // O^T buffer b at column 64 + 16*b
+  const uint32_t tmem_s = tmem_base;            // S^T of group g at column 32*g (+16 for tg = 1)
+  const uint32_t tmem_o = tmem_base + kTmemO;   // O^T of group g, parity b at column 32*g + 16*b
 
   const int n_items = n_sp * p.Hkv;
   const int first = blockIdx.x;
@@ -216,7 +237,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
   // Tuning aid: when p.trace is set, lane 0 of each role of CTA 0 stamps the SM clock at a few
   // points of its first 64 items: trace[(role * 64 + item) * 4 + point].
   auto stamp = [&](int role, int item, int point) {
-    if (p.trace != nullptr && blockIdx.x == 0 && lane == 0 && item < 64)
+    if (TRACE && p.trace != nullptr && blockIdx.x == 0 && lane == 0 && item < 64)
       p.trace[(role * 64 + item) * 4 + point] = (unsigned long long)clock64();
   };
   auto fail = [&]() {
@@ -234,7 +255,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
     const uint8_t* cache = is_v ? p.v : p.k;
     const int64_t stride_block = is_v ? p.v_stride_block : p.k_stride_block;
     const int64_t stride_head = is_v ? p.v_stride_head : p.k_stride_head;
-    const int full0 = is_v ? kBarVFull : kBarKFull, empty0 = is_v ? kBarVEmpty : kBarKEmpty;
+    const int full0 = is_v ? kBarVFull : kBarKQFull;
     const uint64_t pol = l2_policy_evict_first();
     auto load_page_id = [&](const Item& it) -> int {
       int id = 0;
@@ -264,9 +285,18 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
         pid_next = load_page_id(it_next);
       }
       const int slot = i % NS;
-      const uint32_t use = (uint32_t)(i / NS);
       stamp(is_v ? 1 : 0, i, 0);
-      if (!wait(bar(empty0, slot), (use & 1) ^ 1)) { fail(); break; }
+      if (i >= NS) {
+        // The slot is free once the product that read it (item i - NS) is complete: QK^T for K
+        // pages, P.V for V pages.  This role has already seen the products of all earlier items,
+        // so the barrier's previous phase is known to be complete.
+        const int j = i - NS;
+        const int g = j % NG;
+        const uint32_t gu = (uint32_t)(j / NG);
+        const bool ok = is_v ? wait(bar(kBarOFull, 2 * g + (int)(gu & 1)), (gu >> 1) & 1)
+                             : wait(bar(kBarSFull, g), gu & 1);
+        if (!ok) { fail(); break; }
+      }
       stamp(is_v ? 1 : 0, i, 1);
       const uint32_t full = bar(full0, slot);
       if (lane == 0) mbar_arrive_expect_tx(full, it.npages * kPageBytes);
@@ -400,24 +430,30 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       }
       fence_proxy_async();  // the tile is read by the tensor core (async proxy)
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarQFull, slot));
+      if (lane == 0) mbar_arrive(bar(kBarKQFull, slot));
       stamp(2, i, 2);
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issue
     constexpr uint32_t kIdesc = idesc_f32acc(128, kNQ, 0, 0);
     const bool leader = elect_one();  // the one lane that issues every MMA and commit
-    for (int i = 0; i <= n_local && !dead; ++i) {
+    // per item i: group g = i % NG, use gu = i / NG of the group's buffers, O^T parity gu & 1.
+    // P.V of an item is issued kLag items after its QK^T, so a softmax group has that long to
+    // turn S^T into P^T before this in-order issue loop would have to wait for it.  The S^T
+    // columns QK^T(i) overwrites were read by the softmax of item i - NG, whose P.V was issued
+    // one iteration ago (kLag = NG - 1), after that group's arrival.
+    constexpr int kLag = NG - 1;
+    for (int i = 0; i < n_local + kLag && !dead; ++i) {
       if (i < n_local) {  // S^T(i) = K . Q^T
-        const int slot = i % NS, buf = i & 1;
+        const int slot = i % NS, g = i % NG;
         const uint32_t use = (uint32_t)(i / NS);
         stamp(3, i, 0);
-        if (!wait(bar(kBarKFull, slot), use & 1) || !wait(bar(kBarQFull, slot), use & 1)) { fail(); break; }
+        if (!wait(bar(kBarKQFull, slot), use & 1)) { fail(); break; }
         stamp(3, i, 1);
         fence_after_sync();
         const uint64_t kd = smem_desc(kv_ring + slot * kSlotBytes, 256, kPageBytes);
         const uint64_t qd = smem_desc(q_ring + slot * kQSlotBytes, 128, 1024);
-        const uint32_t d0 = tmem_s + buf * 32;
+        const uint32_t d0 = tmem_s + g * 32;
 #pragma unroll
         for (int tg = 0; tg < 2; ++tg) {
 #pragma unroll
@@ -427,46 +463,40 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
             if (leader) mma_f8_ss(d0 + tg * 16, ad, bd, kIdesc, j > 0);
           }
         }
-        if (leader) {
-          mma_commit(bar(kBarKEmpty, slot));
-          mma_commit(bar(kBarQEmpty, slot));
-          mma_commit(bar(kBarSFull, buf));
-        }
+        if (leader) mma_commit(bar(kBarSFull, g));
         __syncwarp();
       }
-      if (i >= 1) {  // O^T(i-1) = V^T . P^T
-        const int j = i - 1;
-        const int slot = j % NS, buf = j & 1;
-        const uint32_t use = (uint32_t)(j / NS), buse = (uint32_t)(j >> 1);
-        if (!wait(bar(kBarPFull, buf), buse & 1) || !wait(bar(kBarVFull, slot), use & 1) ||
-            !wait(bar(kBarOEmpty, buf), (buse & 1) ^ 1)) { fail(); break; }
+      if (i >= kLag) {  // O^T(j) = V^T . P^T
+        const int j = i - kLag;
+        const int slot = j % NS, g = j % NG;
+        const uint32_t gu = (uint32_t)(j / NG);
+        const int ob = 2 * g + (int)(gu & 1);
+        // The group arrives here only after it has seen the item's V pages land and after its
+        // epilogue of two items ago has read the O^T columns this product overwrites.
+        if (!wait(bar(kBarPFull, g), gu & 1)) { fail(); break; }
         stamp(3, j, 2);
         fence_after_sync();
         const uint64_t vd = smem_desc(kv_ring + slot * kSlotBytes + kHalfSlot, kPageBytes, 128);
-        const uint64_t pd = smem_desc(p_tiles + buf * kPTileBytes, 128, 256);
-        const uint32_t d0 = tmem_o + buf * 16;
+        const uint64_t pd = smem_desc(p_tiles + g * kPTileBytes, kPLbo, kPSbo);
+        const uint32_t d0 = tmem_o + ob * 16;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint64_t ad = vd + (uint64_t)(((2 * ks) * kPageBytes) >> 4);
-          const uint64_t bd = pd + (uint64_t)((ks * 512) >> 4);
+          const uint64_t bd = pd + (uint64_t)((ks * kPStep) >> 4);
           if (leader) mma_f8_ss(d0, ad, bd, kIdesc, ks > 0);
         }
-        if (leader) {
-          mma_commit(bar(kBarVEmpty, slot));
-          mma_commit(bar(kBarOFull, buf));
-        }
+        if (leader) mma_commit(bar(kBarOFull, ob));
         __syncwarp();
         stamp(3, j, 3);
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue groups
-    const int grp = warp >> 2;         // group 0: warps 0-3, group 1: warps 4-7; owns TMEM buffer grp
+    const int grp = warp >> 2;         // softmax group: takes items grp, grp + NG, ...
     const int wq = warp & 3;           // TMEM lane quarter this warp may touch
     const int r = wq * 32 + lane;      // TMEM lane: S^T row (token slot) / O^T row (head dim)
     const int pg = r >> 3;             // page of the tokens this thread owns in S^T
-    const int buf = grp;
-    const int bar_a = 1 + 2 * grp, bar_b = 2 + 2 * grp;  // named barriers of the group
+    const int bar_a = 1 + grp, bar_b = 1 + kMaxGroups + grp;  // named barriers of the group
     const uint32_t lane_field = (uint32_t)(wq * 32) << 16;
     float k_scale_t = 1.0f, v_scale_t = 1.0f;
     if (!PER_TOKEN && p.kv_quant_mode == PA_QUANT_PER_TENSOR) {
@@ -478,13 +508,18 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
     int lim_off[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) lim_off[q] = q < p.eqG ? (p.L - 1 - q / p.G) : -0x40000000;
-    float* rm = red_max + buf * 32;
+    float* rm = red_max + grp * 32;
 
     auto softmax = [&](int i, const Item& it) -> bool {
       const int slot = i % NS;
-      const uint32_t use = (uint32_t)(i / NS), buse = (uint32_t)(i >> 1);
-      const int par = buf * 2 + (int)(buse & 1);  // double-buffer index of what the epilogue reads
-      if (!wait(bar(kBarQFull, slot), use & 1)) return false;
+      const uint32_t use = (uint32_t)(i / NS), gu = (uint32_t)(i / NG);
+      const int par = grp * 2 + (int)(gu & 1);  // double-buffer index of what the epilogue reads
+      if (wq == 0) stamp(4, i, 0);
+      if (!wait(bar(kBarSFull, grp), gu & 1)) return false;
+      if (wq == 0) stamp(4, i, 1);
+      // QK^T of the item is done, so its query tile was complete: this wait returns at once and
+      // orders the producer's scale writes before the reads below.
+      if (!wait(bar(kBarKQFull, slot), use & 1)) return false;
       const uint32_t aux = q_ring + slot * kQSlotBytes + kQTileBytes;
       float row_scale[8];
       {
@@ -505,13 +540,10 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarQEmpty, slot));
 
-      if (wq == 0) stamp(4, i, 0);
-      if (!wait(bar(kBarSFull, buf), buse & 1)) return false;
-      if (wq == 0) stamp(4, i, 1);
       fence_after_sync();
       uint32_t sraw[2][16];
-      tmem_ld16(tmem_s + lane_field + buf * 32, sraw[0]);
-      tmem_ld16(tmem_s + lane_field + buf * 32 + 16, sraw[1]);
+      tmem_ld16(tmem_s + lane_field + grp * 32, sraw[0]);
+      tmem_ld16(tmem_s + lane_field + grp * 32 + 16, sraw[1]);
       tmem_ld_wait();
       if (wq == 0) stamp(6, i, 0);
 
@@ -538,14 +570,14 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       }
       if (PER_TOKEN) {
         const int vk = __reduce_max_sync(kFullMask, float_to_ordered(fmaxf(vs_tok[0], vs_tok[1])));
-        if (lane == 0) v_max[buf * 4 + wq] = ordered_to_float(vk);
+        if (lane == 0) v_max[grp * 4 + wq] = ordered_to_float(vk);
       }
       if (wq == 0) stamp(6, i, 1);
       named_barrier_sync(bar_a, 128);
       if (wq == 0) stamp(6, i, 2);
       float vinv = 1.0f, vnorm = 1.0f;
       if (PER_TOKEN) {
-        const float4 vm4 = *reinterpret_cast<const float4*>(v_max + buf * 4);
+        const float4 vm4 = *reinterpret_cast<const float4*>(v_max + grp * 4);
         vnorm = fmaxf(fmaxf(vm4.x, vm4.y), fmaxf(vm4.z, vm4.w));
         vinv = vnorm > 0.f ? 1.0f / vnorm : 0.f;
       }
@@ -573,21 +605,29 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
           pbytes[tg][3] = pack_e4m3x4(lo[tg][4], lo[tg][5], lo[tg][6], lo[tg][7]);
         }
       }
+      // The group's P^T tile is still being read by P.V of the group's previous item until that
+      // product's commit has arrived (normally long ago).
+      if (gu > 0) {
+        const uint32_t pu = gu - 1;
+        if (!wait(bar(kBarOFull, 2 * grp + (int)(pu & 1)), (pu >> 1) & 1)) return false;
+      }
       // P^T tile of k-step pg/2: [row block (hi | lo)][K unit = pg % 2][row q][token]
-      const uint32_t pt = p_tiles + buf * kPTileBytes + (pg >> 1) * 512 + (pg & 1) * 128 + (r & 7);
+      const uint32_t pt = p_tiles + grp * kPTileBytes + (pg >> 1) * kPStep + (pg & 1) * kPLbo + (r & 7);
 #pragma unroll
       for (int tg = 0; tg < 2; ++tg) {
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
           sts8(pt + q * 16 + tg * 8, pbytes[tg][q >> 2] >> (8 * (q & 3)));
-          sts8(pt + 256 + q * 16 + tg * 8, pbytes[tg][2 + (q >> 2)] >> (8 * (q & 3)));
+          sts8(pt + kPSbo + q * 16 + tg * 8, pbytes[tg][2 + (q >> 2)] >> (8 * (q & 3)));
         }
       }
       if (wq == 0) stamp(6, i, 3);
       // Bytes of V past the context (absent pages, tokens past the end of the last page) may
       // hold anything, NaN patterns included, and 0 * NaN would poison O^T: clear them.
+      // (P.V of the previous item in this slot was issued before QK^T of this one, so the V
+      // barrier's previous phase is complete.)
+      if (!wait(bar(kBarVFull, slot), use & 1)) return false;
       if (it.ntok < kItemTokens) {
-        if (!wait(bar(kBarVFull, slot), use & 1)) return false;
         const uint32_t vrow = kv_ring + slot * kSlotBytes + kHalfSlot + r * 16;  // row = head dim r
         const int first_bad = it.ntok >> 4;           // page holding the first invalid token
         const int keep = it.ntok & 15;                // valid tokens in that page
@@ -609,7 +649,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       fence_proxy_async();   // P^T and the cleared V bytes are read by the tensor core
       fence_before_sync();   // the S^T loads above are complete (tmem_ld_wait)
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarPFull, buf));
+      if (lane == 0) mbar_arrive(bar(kBarPFull, grp));
       if (wq == 0) stamp(4, i, 2);
       // row sums, needed only by the epilogue of this item
       const float wsum = warp_reduce8<false>(psum, lane);
@@ -618,21 +658,21 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       return true;
     };
 
-    auto epilogue = [&](int j, const Item& it) -> bool {
-      const uint32_t buse = (uint32_t)(j >> 1);
-      const int par = buf * 2 + (int)(buse & 1);
+    // `tail`: no softmax of a later item of this group ran in between, so the row sums of item j
+    // still need a barrier of their own to be visible to the whole group.
+    auto epilogue = [&](int j, const Item& it, bool tail) -> bool {
+      const uint32_t gu = (uint32_t)(j / NG);
+      const int par = grp * 2 + (int)(gu & 1);
       const float* rs = red_sum + par * 32;
-      named_barrier_sync(bar_b, 128);  // the row sums of item j are complete and visible
+      if (tail) named_barrier_sync(bar_b, 128);
       if (wq == 0) stamp(5, j, 0);
-      if (!wait(bar(kBarOFull, buf), buse & 1)) return false;
+      if (!wait(bar(kBarOFull, par), (gu >> 1) & 1)) return false;
       if (wq == 0) stamp(5, j, 1);
       fence_after_sync();
       uint32_t oraw[16];
-      tmem_ld16(tmem_o + lane_field + buf * 16, oraw);
+      tmem_ld16(tmem_o + lane_field + par * 16, oraw);
       tmem_ld_wait();
-      fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarOEmpty, buf));
+      fence_before_sync();  // ordered before this warp's next arrival on the group's P barrier
       if (wq == 0) stamp(7, j, 0);
 
       const float vfin = PER_TOKEN ? v_norm[par] : v_scale_t;
@@ -658,21 +698,21 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       return true;
     };
 
-    // group g walks the CTA's items g, g+2, ...; the epilogue of an item runs after the softmax
+    // group g walks the CTA's items g, g+NG, ...; the epilogue of an item runs after the softmax
     // of the group's next item, by which time its P.V product has long been issued
     ItemCursor cur;
-    if (grp < n_local) cur.init(first + grp * stride, 2 * stride, p, seq_off);
+    if (grp < n_local) cur.init(first + grp * stride, NG * stride, p, seq_off);
     Item it_prev{};
     int prev = -1;
-    for (int i = grp; i < n_local && !dead; i += 2) {
+    for (int i = grp; i < n_local && !dead; i += NG) {
       const Item it = cur.item(p, seq_off, seq_ctx);
       cur.advance(p, seq_off);
       if (!softmax(i, it)) { fail(); break; }
-      if (prev >= 0 && !epilogue(prev, it_prev)) { fail(); break; }
+      if (prev >= 0 && !epilogue(prev, it_prev, false)) { fail(); break; }
       it_prev = it;
       prev = i;
     }
-    if (!dead && prev >= 0 && !epilogue(prev, it_prev)) fail();
+    if (!dead && prev >= 0 && !epilogue(prev, it_prev, true)) fail();
   }
 
   // ---------------------------------------------------------------------- teardown
