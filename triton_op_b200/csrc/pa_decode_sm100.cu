@@ -188,10 +188,13 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
     k.off_seq_ctx = off + round_up((p->num_seqs + 1) * 4, 16);
     off = round_up(off + index_bytes, 128);
     k.off_q = off;
+    // The ring must be deeper than the distance by which P.V trails QK^T in the issue loop: the
+    // barrier waits of the pipeline are only valid under that condition.
+    constexpr int kMinSlots = pa::tc::kNG;
     int slots = pa::tc::kMaxSlots;
-    if (p->tune_stages > 0 && p->tune_stages < slots) slots = p->tune_stages;
+    if (p->tune_stages >= kMinSlots && p->tune_stages < slots) slots = p->tune_stages;
     const int qslot = pa::tc::q_slot_bytes(per_token);
-    for (; slots >= 2; --slots) {
+    for (; slots >= kMinSlots; --slots) {
       const int off_p = round_up(off + slots * qslot, 128);
       const int ring = round_up(off_p + pa::tc::kNG * pa::tc::kPTileBytes, 1024);
       if (ring + slots * pa::tc::kSlotBytes <= dev->max_smem_optin) {
@@ -200,7 +203,7 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
         break;
       }
     }
-    if (slots < 2) return PA_ERR_TOO_LARGE;  // num_seqs too large for the in-kernel index
+    if (slots < kMinSlots) return PA_ERR_TOO_LARGE;  // num_seqs too large for the in-kernel index
     k.num_stages = slots;
     plan->smem = k.off_ring + slots * pa::tc::kSlotBytes;
     int64_t grid = items_cap < dev->sm_count ? items_cap : dev->sm_count;
@@ -254,9 +257,9 @@ int launch_partition_t(const LaunchPlan& plan, cudaStream_t stream) {
   return PA_OK;
 }
 
-template <bool PT, bool TRACE>
+template <bool PT, bool TRACE, int QR>
 int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
-  auto kern = pa::tc::pa_partition_fp8_tc_kernel<PT, TRACE>;
+  auto kern = pa::tc::pa_partition_fp8_tc_kernel<PT, TRACE, QR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
   if (e != cudaSuccess) return cuda_fail(e);
   kern<<<plan.grid, pa::tc::kThreads, plan.smem, stream>>>(plan.kp);
@@ -268,9 +271,13 @@ int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
 int launch_partition(const LaunchPlan& plan, cudaStream_t stream) {
   if (plan.kp.S == 0) return PA_OK;
   if (plan.tensor_path) {
-    if (plan.kp.trace != nullptr)  // tuning build of the kernel with the clock stamps compiled in
-      return plan.per_token ? launch_tensor_t<true, true>(plan, stream) : launch_tensor_t<false, true>(plan, stream);
-    return plan.per_token ? launch_tensor_t<true, false>(plan, stream) : launch_tensor_t<false, false>(plan, stream);
+    const bool r4 = plan.kp.eqG <= 4;  // the softmax handles 4 query rows instead of 8
+    if (plan.kp.trace != nullptr) {  // tuning build of the kernel with the clock stamps compiled in
+      if (plan.per_token) return r4 ? launch_tensor_t<true, true, 4>(plan, stream) : launch_tensor_t<true, true, 8>(plan, stream);
+      return r4 ? launch_tensor_t<false, true, 4>(plan, stream) : launch_tensor_t<false, true, 8>(plan, stream);
+    }
+    if (plan.per_token) return r4 ? launch_tensor_t<true, false, 4>(plan, stream) : launch_tensor_t<true, false, 8>(plan, stream);
+    return r4 ? launch_tensor_t<false, false, 4>(plan, stream) : launch_tensor_t<false, false, 8>(plan, stream);
   }
 #define PA_CASE(NW, MT, PT) \
   if (plan.warps == NW && plan.mtiles == MT && plan.per_token == PT) return launch_partition_t<NW, MT, PT>(plan, stream);

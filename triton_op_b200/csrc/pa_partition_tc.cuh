@@ -178,8 +178,29 @@ __device__ __forceinline__ float warp_reduce8(const float (&v)[8], int lane) {
   return c;
 }
 
+// Six shuffles for four values; lane ends up with the result for q = (lane >> 3) & 3.
+template <bool IS_MAX>
+__device__ __forceinline__ float warp_reduce4(const float (&v)[4], int lane) {
+  auto op = [](float a, float b) { return IS_MAX ? fmaxf(a, b) : a + b; };
+  const bool b4 = lane & 16, b3 = lane & 8;
+  float a[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float mine = b4 ? v[2 + j] : v[j];
+    const float other = b4 ? v[j] : v[2 + j];
+    a[j] = op(mine, __shfl_xor_sync(kFullMask, other, 16));
+  }
+  float c = op(b3 ? a[1] : a[0], __shfl_xor_sync(kFullMask, b3 ? a[0] : a[1], 8));
+  c = op(c, __shfl_xor_sync(kFullMask, c, 4));
+  c = op(c, __shfl_xor_sync(kFullMask, c, 2));
+  c = op(c, __shfl_xor_sync(kFullMask, c, 1));
+  return c;
+}
+
 // PER_TOKEN: per-token-per-head K/V scales.  TRACE: compile the clock stamps in (tuning builds).
-template <bool PER_TOKEN, bool TRACE>
+// QR: query rows the softmax handles (4 or 8, >= eqG).  Row q sits in tile row / TMEM column q
+// (hi half) and QR + q (lo half), so with QR = 4 only the first row block is ever touched.
+template <bool PER_TOKEN, bool TRACE, int QR>
 __global__ void __launch_bounds__(kThreads, 1)
 pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
   constexpr int NG = kNG;
@@ -412,11 +433,14 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
           hi4[k] = pack_e4m3x4(hi[0], hi[1], hi[2], hi[3]);
           lo4[k] = pack_e4m3x4(lo[0], lo[1], lo[2], lo[3]);
         }
-        const uint32_t dst = qt + (2 * qq + c) * 128 + n0 * 16;
-        sts128(dst, make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]));          // row block 0: hi rows
-        sts128(dst + 1024, make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]));   // row block 1: lo rows
+        if (n0 < QR) {  // tile row n0 holds the hi half, tile row QR + n0 the lo half
+          const int nl = QR + n0;
+          const uint32_t dst = qt + (2 * qq + c) * 128;
+          sts128(dst + n0 * 16, make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]));
+          sts128(dst + (nl >> 3) * 1024 + (nl & 7) * 16, make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]));
+        }
       }
-      if (qq == 0) {
+      if (qq == 0 && n0 < QR) {
         float qs = 1.0f;
         if (p.q_quant_mode == PA_QUANT_PER_TENSOR) qs = __ldg(p.q_scale);
         if (p.q_quant_mode == PA_QUANT_PER_TOKEN && row_ok)
@@ -442,7 +466,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
     // turn S^T into P^T before this in-order issue loop would have to wait for it.  The S^T
     // columns QK^T(i) overwrites were read by the softmax of item i - NG, whose P.V was issued
     // one iteration ago (kLag = NG - 1), after that group's arrival.
-    constexpr int kLag = NG - 1;
+    constexpr int kLag = NG - 1;  // the host guarantees num_stages > kLag
     for (int i = 0; i < n_local + kLag && !dead; ++i) {
       if (i < n_local) {  // S^T(i) = K . Q^T
         const int slot = i % NS, g = i % NG;
@@ -505,9 +529,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
     }
     const float base_scale = p.softmax_scale * kLog2e * k_scale_t;
     // row q sees token j iff j < ctx - lim_off[q]; padding rows see nothing
-    int lim_off[8];
+    int lim_off[QR];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) lim_off[q] = q < p.eqG ? (p.L - 1 - q / p.G) : -0x40000000;
+    for (int q = 0; q < QR; ++q) lim_off[q] = q < p.eqG ? (p.L - 1 - q / p.G) : -0x40000000;
     float* rm = red_max + grp * 32;
 
     auto softmax = [&](int i, const Item& it) -> bool {
@@ -521,12 +545,13 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       // orders the producer's scale writes before the reads below.
       if (!wait(bar(kBarKQFull, slot), use & 1)) return false;
       const uint32_t aux = q_ring + slot * kQSlotBytes + kQTileBytes;
-      float row_scale[8];
+      float row_scale[QR];
       {
-        const uint4 a = lds128(aux), b = lds128(aux + 16);
+        const uint4 a = lds128(aux);
+        const uint4 b = QR > 4 ? lds128(aux + 16) : make_uint4(0u, 0u, 0u, 0u);
         const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-        for (int q = 0; q < 8; ++q) row_scale[q] = __uint_as_float(w[q]) * base_scale;
+        for (int q = 0; q < QR; ++q) row_scale[q] = __uint_as_float(w[q]) * base_scale;
       }
       float ks_tok[2] = {1.f, 1.f}, vs_tok[2] = {1.f, 1.f};
       if (PER_TOKEN) {
@@ -541,21 +566,21 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       if (lane == 0) mbar_arrive(bar(kBarQEmpty, slot));
 
       fence_after_sync();
-      uint32_t sraw[2][16];
-      tmem_ld16(tmem_s + lane_field + grp * 32, sraw[0]);
-      tmem_ld16(tmem_s + lane_field + grp * 32 + 16, sraw[1]);
+      uint32_t sraw[2][2 * QR];  // columns: hi halves of the QR rows, then their lo halves
+      tmem_ld(tmem_s + lane_field + grp * 32, sraw[0]);
+      tmem_ld(tmem_s + lane_field + grp * 32 + 16, sraw[1]);
       tmem_ld_wait();
       if (wq == 0) stamp(6, i, 0);
 
-      float s[2][8];
-      int key[8];
+      float s[2][QR];
+      int key[QR];
 #pragma unroll
       for (int tg = 0; tg < 2; ++tg) {
         const int tok = it.tok0 + pg * 16 + tg * 8 + (r & 7);  // global token index
         const int room = it.ctx - tok;                         // > lim_off[q]  <=>  visible
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          float v = fmaf(__uint_as_float(sraw[tg][8 + q]), 0.0625f, __uint_as_float(sraw[tg][q])) * row_scale[q];
+        for (int q = 0; q < QR; ++q) {
+          float v = fmaf(__uint_as_float(sraw[tg][QR + q]), 0.0625f, __uint_as_float(sraw[tg][q])) * row_scale[q];
           if (PER_TOKEN) v *= ks_tok[tg];
           s[tg][q] = (room > lim_off[q] && lim_off[q] >= 0) ? v : -INFINITY;
         }
@@ -563,10 +588,10 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       }
       // partition maximum per row: integer warp reduction on order-preserving keys
 #pragma unroll
-      for (int q = 0; q < 8; ++q) key[q] = __reduce_max_sync(kFullMask, float_to_ordered(fmaxf(s[0][q], s[1][q])));
+      for (int q = 0; q < QR; ++q) key[q] = __reduce_max_sync(kFullMask, float_to_ordered(fmaxf(s[0][q], s[1][q])));
       if (lane == 0) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) rm[q * 4 + wq] = ordered_to_float(key[q]);
+        for (int q = 0; q < QR; ++q) rm[q * 4 + wq] = ordered_to_float(key[q]);
       }
       if (PER_TOKEN) {
         const int vk = __reduce_max_sync(kFullMask, float_to_ordered(fmaxf(vs_tok[0], vs_tok[1])));
@@ -581,12 +606,12 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
         vnorm = fmaxf(fmaxf(vm4.x, vm4.y), fmaxf(vm4.z, vm4.w));
         vinv = vnorm > 0.f ? 1.0f / vnorm : 0.f;
       }
-      float psum[8];
-      uint32_t pbytes[2][4];  // [tg][hi rows 0-3, hi rows 4-7, lo rows 0-3, lo rows 4-7]
+      float psum[QR];
+      uint32_t pbytes[2][QR / 2];  // [tg][hi rows (QR/4 words), lo rows (QR/4 words)], row q = byte q % 4
       {
-        float hi[2][8], lo[2][8];
+        float hi[2][QR], lo[2][QR];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < QR; ++q) {
           const float4 m4 = *reinterpret_cast<const float4*>(rm + q * 4);
           const float m = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w));
           const float m_use = (m == -INFINITY) ? 0.f : m;
@@ -599,10 +624,11 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
         }
 #pragma unroll
         for (int tg = 0; tg < 2; ++tg) {
-          pbytes[tg][0] = pack_e4m3x4(hi[tg][0], hi[tg][1], hi[tg][2], hi[tg][3]);
-          pbytes[tg][1] = pack_e4m3x4(hi[tg][4], hi[tg][5], hi[tg][6], hi[tg][7]);
-          pbytes[tg][2] = pack_e4m3x4(lo[tg][0], lo[tg][1], lo[tg][2], lo[tg][3]);
-          pbytes[tg][3] = pack_e4m3x4(lo[tg][4], lo[tg][5], lo[tg][6], lo[tg][7]);
+#pragma unroll
+          for (int w = 0; w < QR / 4; ++w) {
+            pbytes[tg][w] = pack_e4m3x4(hi[tg][4 * w], hi[tg][4 * w + 1], hi[tg][4 * w + 2], hi[tg][4 * w + 3]);
+            pbytes[tg][QR / 4 + w] = pack_e4m3x4(lo[tg][4 * w], lo[tg][4 * w + 1], lo[tg][4 * w + 2], lo[tg][4 * w + 3]);
+          }
         }
       }
       // The group's P^T tile is still being read by P.V of the group's previous item until that
@@ -616,9 +642,10 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
 #pragma unroll
       for (int tg = 0; tg < 2; ++tg) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < QR; ++q) {
+          constexpr int kLoBlock = (QR >= 8) ? kPSbo : 0;  // tile row QR + q: row block, then row
           sts8(pt + q * 16 + tg * 8, pbytes[tg][q >> 2] >> (8 * (q & 3)));
-          sts8(pt + kPSbo + q * 16 + tg * 8, pbytes[tg][2 + (q >> 2)] >> (8 * (q & 3)));
+          sts8(pt + kLoBlock + ((QR + q) & 7) * 16 + tg * 8, pbytes[tg][QR / 4 + (q >> 2)] >> (8 * (q & 3)));
         }
       }
       if (wq == 0) stamp(6, i, 3);
@@ -652,8 +679,13 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       if (lane == 0) mbar_arrive(bar(kBarPFull, grp));
       if (wq == 0) stamp(4, i, 2);
       // row sums, needed only by the epilogue of this item
-      const float wsum = warp_reduce8<false>(psum, lane);
-      if ((lane & 3) == 0) red_sum[par * 32 + ((lane >> 2) & 7) * 4 + wq] = wsum;
+      if constexpr (QR == 8) {
+        const float wsum = warp_reduce8<false>(psum, lane);
+        if ((lane & 3) == 0) red_sum[par * 32 + ((lane >> 2) & 7) * 4 + wq] = wsum;
+      } else {
+        const float wsum = warp_reduce4<false>(psum, lane);
+        if ((lane & 7) == 0) red_sum[par * 32 + ((lane >> 3) & 3) * 4 + wq] = wsum;
+      }
       if (PER_TOKEN && r == 0) v_norm[par] = vnorm;
       return true;
     };
@@ -669,8 +701,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       if (!wait(bar(kBarOFull, par), (gu >> 1) & 1)) return false;
       if (wq == 0) stamp(5, j, 1);
       fence_after_sync();
-      uint32_t oraw[16];
-      tmem_ld16(tmem_o + lane_field + par * 16, oraw);
+      uint32_t oraw[2 * QR];
+      tmem_ld(tmem_o + lane_field + par * 16, oraw);
       tmem_ld_wait();
       fence_before_sync();  // ordered before this warp's next arrival on the group's P barrier
       if (wq == 0) stamp(7, j, 0);
@@ -681,12 +713,12 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
       unsigned short* tmp = reinterpret_cast<unsigned short*>(p.tmp_out) + (int64_t)it.seq * p.tmp_stride_seq +
                             (int64_t)it.head * p.tmp_stride_head + (int64_t)it.part * p.tmp_stride_part + r;
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
+      for (int q = 0; q < QR; ++q) {
         if (q < p.eqG) {
           const float4 l4 = *reinterpret_cast<const float4*>(rs + q * 4);
           const float l = (l4.x + l4.y) + (l4.z + l4.w);   // in units of 1/256
           const float f = l > 0.f ? __fdividef(vfin, l) : 0.f;
-          const float o = fmaf(__uint_as_float(oraw[8 + q]), 0.0625f, __uint_as_float(oraw[q])) * f;
+          const float o = fmaf(__uint_as_float(oraw[QR + q]), 0.0625f, __uint_as_float(oraw[q])) * f;
           tmp[(int64_t)q * p.tmp_stride_row] = (unsigned short)(pack_bf16x2(o, 0.f) & 0xffffu);
           if (r == q) {
             p.max_logits[ws_base + q] = m_fin[par * 8 + q] * kLn2;
