@@ -1,0 +1,369 @@
+#!/usr/bin/env python
+"""Benchmark of the paged-attention decode operator.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    torchrun --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+
+A step is one decode call (partition kernel + reduce kernel) over one batch of synthetic input.
+The workload at every N is the Llama-3-8B-shaped configuration the headline metric is quoted on
+(64 sequences x 4096 tokens, 32 query / 8 kv heads, fp8 KV, 16-token pages) per GPU: sequences
+are independent, so ranks shard the batch with no collective and the scaling is weak.
+
+One JSON line is printed by rank 0:
+  value      KV bytes all ranks read per step / device time of the step (max over ranks), inputs
+             resident in HBM;
+  e2e        the same metric through the public entry point with the step's inputs (query, block
+             tables, context lengths) coming from pinned host memory and the output copied back;
+  roofline   the partition kernel alone against the measured HBM copy bandwidth;
+  cpu_baseline  the oracle (a CPU port of the reference's own PyTorch path) on a bounded sample.
+`--impl reference` times that CPU path as the reference arm (rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from triton_op_b200.inputs import CONFIGS, make_inputs  # noqa: E402
+
+METRIC = "kv_read_hbm_bandwidth"
+UNIT = "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one partition-kernel launch divided by the
+# algorithmic KV bytes of that launch, from the ncu capture summarised in
+# profiles/partition_kernel_tcgen05_llama8b.md (32-sequence case; traffic grows in proportion).
+NCU_TRAFFIC_PER_KV_BYTE = 1.021
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "20"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        mhz, mx, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clk = float(parts[0])
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            if clk > 0.5 * mx:  # samples taken while the GPU was under load
+                mhz.append(clk)
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx,
+                "samples_under_load": len(mhz), "reasons": sorted(reasons)}
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29531")
+        dist.init_process_group("nccl" if torch.cuda.is_available() else "gloo",
+                                rank=rank, world_size=world,
+                                device_id=torch.device(f"cuda:{local}") if torch.cuda.is_available() else None)
+    return rank, world, local
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def max_over_ranks(x: float, world: int, device) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(x: float, world: int, device) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_reference_time(inp_cpu, sample_seqs: int, repeats: int = 1):
+    """Times the oracle (CPU port of the reference's PyTorch path) on the first `sample_seqs`
+    sequences of the workload.  Returns (seconds per pass, KV bytes of the sample, threads)."""
+    from oracle import pa_oracle  # checker / CPU baseline only; never on the product path
+    c = inp_cpu.cfg
+    n = min(sample_seqs, c.num_seqs)
+    L = c.query_len
+    ks, vs = inp_cpu.flat_scales()
+    q = inp_cpu.query_tokens[: n * L]
+    bt = inp_cpu.block_tables[:n]
+    ctx = inp_cpu.context_lens[:n]
+    indptr = torch.arange(n + 1, dtype=torch.int32) * L
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        pa_oracle.paged_attention(q, inp_cpu.key_cache, inp_cpu.value_cache, bt, ctx, indptr, ks, vs)
+        best = min(best, time.perf_counter() - t0)
+    item = inp_cpu.key_cache.element_size()
+    kv_bytes = int(ctx.to(torch.int64).sum().item()) * c.kv_heads * c.head_size * 2 * item
+    return best, kv_bytes, torch.get_num_threads()
+
+
+def run_reference_arm(args, rank: int, world: int):
+    """The reference's own CPU implementation of the path, on this box's host cores."""
+    if rank != 0:
+        return
+    cfg = CONFIGS[args.workload]
+    sample = 8
+    # only the sample's pages are materialised: the pool is exactly what the sample uses
+    small = type(cfg)(**{**cfg.__dict__, "num_seqs": sample, "pool_blocks": None})
+    inp = make_inputs(small, seed=0, device="cpu")
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_reference_time(inp, sample)
+    times = []
+    kvb = 0
+    for _ in range(args.steps):
+        t, kvb, thr = cpu_reference_time(inp, sample)
+        times.append(t)
+    t_step = sum(times) / len(times)
+    value = kvb / t_step / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_step * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "sample": f"first {sample} of {cfg.num_seqs} sequences per step",
+                   "kv": "fp8 e4m3fn per-tensor scales", "context_len": cfg.context[1] if cfg.context[0] == "fixed" else str(cfg.context)},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{sample} sequences ({kvb} KV bytes) per step, oracle/pa_oracle.py on host cores"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_ours(args, rank: int, world: int, local: int):
+    import ctypes as C
+    from triton_op_b200 import _lib, paged_attention_decode
+    from triton_op_b200.pa_decode import build_params
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the operator has no CPU path")
+    _lib.lib()  # raises when the CUDA library is missing
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    cfg = CONFIGS[args.workload]
+    inp = make_inputs(cfg, seed=rank, device=dev)          # every rank its own batch (weak scaling)
+    c = inp.cfg
+    out = torch.empty_like(inp.query)
+    status = torch.zeros((), dtype=torch.int32, device=dev)
+
+    def call(query, ctx, bt):
+        paged_attention_decode(out, query, inp.key_cache, inp.value_cache, ctx, bt, inp.softmax_scale,
+                               c.query_len, inp.max_context, torch.bfloat16, None, inp.key_scale,
+                               inp.value_scale, partition_size=c.partition_size, status=status)
+
+    kv_bytes = inp.kv_bytes
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    # ---- device-resident inputs: K steps between two events on the launching stream
+    for _ in range(args.warmup):
+        call(inp.query, inp.context_lens, inp.block_tables)
+    torch.cuda.synchronize()
+    barrier(world)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = ev(), ev()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        call(inp.query, inp.context_lens, inp.block_tables)
+    e1.record()
+    torch.cuda.synchronize()
+    barrier(world)
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps, world, dev)
+
+    # ---- the partition kernel alone (the dominant kernel) for the roofline
+    p, keep = build_params(out, inp.query, inp.key_cache, inp.value_cache, inp.context_lens, inp.block_tables,
+                           inp.softmax_scale, c.query_len, inp.max_context, torch.bfloat16, None,
+                           inp.key_scale, inp.value_scale, None, c.partition_size, None, None, None, status, None)
+    L = _lib.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    n_k = max(20, min(args.steps, 200))
+    k0, k1 = ev(), ev()
+    k0.record()
+    for _ in range(n_k):
+        _lib.check(L.pa_partition_sm100(C.byref(p), stream), "pa_partition_sm100")
+    k1.record()
+    torch.cuda.synchronize()
+    us_partition = k0.elapsed_time(k1) * 1e3 / n_k
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end: the step's inputs arrive from pinned host memory, the output goes back
+    hq = inp.query.cpu().pin_memory()
+    hctx = inp.context_lens.cpu().pin_memory()
+    hbt = inp.block_tables.cpu().pin_memory()
+    hout = torch.empty_like(out, device="cpu").pin_memory()
+    dq, dctx, dbt = torch.empty_like(inp.query), torch.empty_like(inp.context_lens), torch.empty_like(inp.block_tables)
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        dctx.copy_(hctx, non_blocking=True)
+        dbt.copy_(hbt, non_blocking=True)
+        call(dq, dctx, dbt)
+        hout.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # the caller reads the result every step
+
+    for _ in range(max(3, args.warmup // 2)):
+        e2e_step()
+    barrier(world)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    g0, g1 = ev(), ev()
+    g0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    g1.record()
+    torch.cuda.synchronize()
+    ms_e2e = max_over_ranks(max(g0.elapsed_time(g1), (time.perf_counter() - t0) * 1e3) / args.steps, world, dev)
+    h2d = hq.numel() * hq.element_size() + hctx.numel() * 4 + hbt.numel() * 4
+    d2h = hout.numel() * hout.element_size()
+
+    total_kv = sum_over_ranks(float(kv_bytes), world, dev)
+    dev_status = int(status.item())
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peak()
+    achieved = kv_bytes / (us_partition * 1e-6) / 1e9
+    value = total_kv / (ms_step * 1e-3) / 1e9
+
+    # ---- CPU baseline on a bounded sample of the same workload (rank 0, N = 1 only)
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        sample = 8
+        sub = type(cfg)(**{**cfg.__dict__, "num_seqs": sample, "pool_blocks": None})
+        cpu_inp = make_inputs(sub, seed=0, device="cpu")
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
+        cpu_reference_time(cpu_inp, sample)
+        t_cpu, kvb_cpu, threads = cpu_reference_time(cpu_inp, sample, repeats=3)
+        cpu_baseline = {"value": kvb_cpu / t_cpu / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+                        "sample": f"first {sample} of {cfg.num_seqs} sequences ({kvb_cpu} KV bytes), best of 3, "
+                                  f"oracle/pa_oracle.py with torch CPU threads"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "us_per_call": ms_step * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32",
+        "data": "synthetic",
+        "pct_of_nominal_hbm": 100.0 * value / (NOMINAL_HBM_GBS * world),
+        "config": {"workload": args.workload, "num_seqs_per_gpu": c.num_seqs, "q_heads": c.q_heads,
+                   "kv_heads": c.kv_heads, "head_size": c.head_size, "block_size": c.block_size,
+                   "query_len": c.query_len, "context_len": inp.max_context, "kv": "fp8 e4m3fn, per-tensor scales",
+                   "partition_size": c.partition_size, "kv_bytes_per_gpu": kv_bytes,
+                   "l2": "inputs larger than L2 (KV read per step: %.0f MB per GPU)" % (kv_bytes / 1e6),
+                   "sharding": "sequences, no collective"},
+        "roofline": {"bound": "hbm", "kernel": "pa_partition_fp8_tc_kernel", "achieved": achieved, "peak": peak,
+                     "peak_kind": peak_kind + " (torch copy_, read+write)", "unit": "GB/s", "frac": achieved / peak,
+                     "us_per_launch": us_partition, "algorithmic_bytes": kv_bytes,
+                     "traffic": (NCU_TRAFFIC_PER_KV_BYTE * kv_bytes) if NCU_TRAFFIC_PER_KV_BYTE else None},
+        "cpu_baseline": cpu_baseline,
+        "e2e": {"value": total_kv / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "us_per_call": ms_e2e * 1e3,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "note": "query, block tables and context lengths from pinned host memory, output copied back; "
+                        "the KV cache is resident state, as in serving"},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+        "device_status": dev_status,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2_llama8b", choices=sorted(CONFIGS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        rank = int(os.environ.get("RANK", "0"))
+        run_reference_arm(args, rank, int(os.environ.get("WORLD_SIZE", "1")))
+        return
+    rank, world, local = dist_setup(args.gpus)
+    try:
+        run_ours(args, rank, world, local)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
