@@ -169,6 +169,33 @@ int pa_merge_triples_sm100(void* out, int64_t out_stride_row, const float* m, co
 int pa_query_launch_sm100(const PaDecodeParams* params, int32_t* grid_ctas, int32_t* cta_threads,
                           int32_t* smem_bytes, int32_t* ring_stages);
 
+/*
+ * pa_decode_sm100 for callers that must not allocate device memory.  (No counterpart in the
+ * reference, which allocates its three workspaces with torch.zeros on every call.)
+ *
+ * Who needs it: an inference runtime that has handed the whole GPU memory to its own pool, a
+ * plugin running inside somebody else's process where cudaMalloc may fail or stall behind other
+ * streams, or code that may run while a stream is being captured, when allocating is not allowed.
+ * Such a caller passes inputs and `out` as usual and leaves exp_sums / max_logits / tmp_out
+ * NULL (they are ignored): the split-KV workspaces live in a fixed array inside the library,
+ * PA_NOALLOC_SCRATCH_BYTES of device memory that every GPU holds from the moment it loads the
+ * library until the process exits.
+ *
+ * Limits and rules:
+ *  - num_seqs * num_kv_heads * max_partitions * (query_len * query_group_size) rows must fit:
+ *    264 bytes per row (two fp32 + 128 bf16) plus alignment, at most PA_NOALLOC_SCRATCH_BYTES;
+ *    a larger problem returns PA_ERR_TOO_LARGE and launches nothing.
+ *  - The first call on each device looks up the array's device address (with that device
+ *    current).  Make that first call outside any stream capture.
+ *  - All calls on one device share the array and it keeps the last call's contents.  Nothing
+ *    in it has to start at zero (the partition kernel writes every element the reduce reads),
+ *    but two calls that overlap on the GPU -- different streams, or different host threads --
+ *    race on it: serialise them.
+ *  - Neither this function nor anything it calls allocates or frees memory.
+ */
+#define PA_NOALLOC_SCRATCH_BYTES (16u << 20)
+int pa_decode_noalloc_sm100(const PaDecodeParams* params, void* stream);
+
 /* Static string for a PaStatus. */
 const char* pa_strerror(int status);
 

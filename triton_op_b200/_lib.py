@@ -18,9 +18,10 @@ PA_QUANT_NONE, PA_QUANT_PER_TENSOR, PA_QUANT_PER_TOKEN = -1, 0, 1
 PA_V_NORMAL, PA_V_TRANSPOSED = 0, 1
 PA_DEV_WAIT_TIMEOUT, PA_DEV_BAD_PAGE_ID, PA_DEV_CTX_TOO_LONG = 1, 2, 4
 PA_TRACE_WORDS = 8 * 64 * 4
+PA_NOALLOC_SCRATCH_BYTES = 16 << 20
 
 EXPORTS = (
-    "pa_decode_sm100", "pa_partition_sm100", "pa_reduce_sm100", "pa_merge_triples_sm100",
+    "pa_decode_sm100", "pa_decode_noalloc_sm100", "pa_partition_sm100", "pa_reduce_sm100", "pa_merge_triples_sm100",
     "pa_query_launch_sm100", "pa_strerror", "pa_last_cuda_error", "pa_abi_version",
 )
 
@@ -76,11 +77,12 @@ def lib() -> C.CDLL:
     P = C.POINTER(PaDecodeParams)
     L.pa_decode_sm100.argtypes = [P, C.c_void_p]
     L.pa_partition_sm100.argtypes = [P, C.c_void_p]
+    L.pa_decode_noalloc_sm100.argtypes = [P, C.c_void_p]
     L.pa_reduce_sm100.argtypes = [P, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.pa_merge_triples_sm100.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
     L.pa_query_launch_sm100.argtypes = [P] + [C.POINTER(C.c_int32)] * 4
-    for name in ("pa_decode_sm100", "pa_partition_sm100", "pa_reduce_sm100",
+    for name in ("pa_decode_sm100", "pa_decode_noalloc_sm100", "pa_partition_sm100", "pa_reduce_sm100",
                  "pa_merge_triples_sm100", "pa_query_launch_sm100", "pa_last_cuda_error",
                  "pa_abi_version"):
         getattr(L, name).restype = C.c_int

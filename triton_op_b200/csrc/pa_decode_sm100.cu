@@ -5,6 +5,8 @@
 #include <stdint.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "../../include/pa_decode_sm100.h"
 #include "pa_partition_fp8.cuh"
 #include "pa_partition_tc.cuh"
@@ -361,6 +363,62 @@ int pa_decode_sm100(const PaDecodeParams* params, void* stream) {
   rc = launch_partition(plan, static_cast<cudaStream_t>(stream));
   if (rc != PA_OK) return rc;
   return launch_reduce(params, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+// ---- the entry point that allocates nothing -------------------------------------------------
+// The workspaces of the split-KV pass live in this array.  In host code its name is only a
+// handle: the device address is looked up once per device with cudaGetSymbolAddress.
+}  // extern "C"
+namespace {
+static __device__ __align__(256) unsigned char g_noalloc_scratch[PA_NOALLOC_SCRATCH_BYTES];
+std::mutex g_noalloc_mutex;
+unsigned char* g_noalloc_ptr[kMaxDevices] = {};
+
+int noalloc_scratch_address(unsigned char** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e);
+  if (dev < 0 || dev >= kMaxDevices) return PA_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);  // address on the current device
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (ptr == nullptr) return PA_ERR_CUDA;
+    g_noalloc_ptr[dev] = static_cast<unsigned char*>(ptr);
+  }
+  *out = g_noalloc_ptr[dev];
+  return PA_OK;
+}
+}  // namespace
+extern "C" {
+
+int pa_decode_noalloc_sm100(const PaDecodeParams* params, void* stream) {
+  if (!params) return PA_ERR_NULL_POINTER;
+  if (params->struct_size != sizeof(PaDecodeParams) || params->abi_version != PA_ABI_VERSION) return PA_ERR_ABI;
+  if (params->num_seqs < 0 || params->num_kv_heads <= 0 || params->query_group_size <= 0 ||
+      params->query_len <= 0 || params->max_partitions <= 0 || params->head_size != pa::kD)
+    return PA_ERR_BAD_SHAPE;
+  const int64_t eqG = (int64_t)params->query_group_size * params->query_len;
+  const int64_t rows = (int64_t)params->num_seqs * params->num_kv_heads * params->max_partitions * eqG;
+  const int64_t f32_bytes = (rows * 4 + 255) / 256 * 256;       // exp_sums, then max_logits
+  const int64_t need = 2 * f32_bytes + rows * pa::kD * 2;       // then tmp_out (bf16)
+  if (need > (int64_t)PA_NOALLOC_SCRATCH_BYTES) return PA_ERR_TOO_LARGE;
+  unsigned char* base = nullptr;
+  int rc = noalloc_scratch_address(&base);
+  if (rc != PA_OK) return rc;
+  PaDecodeParams q = *params;
+  q.exp_sums = reinterpret_cast<float*>(base);
+  q.max_logits = reinterpret_cast<float*>(base + f32_bytes);
+  q.tmp_out = base + 2 * f32_bytes;
+  q.ws_stride_part = eqG;
+  q.ws_stride_head = eqG * params->max_partitions;
+  q.ws_stride_seq = q.ws_stride_head * params->num_kv_heads;
+  q.tmp_stride_row = pa::kD;
+  q.tmp_stride_part = eqG * pa::kD;
+  q.tmp_stride_head = q.tmp_stride_part * params->max_partitions;
+  q.tmp_stride_seq = q.tmp_stride_head * params->num_kv_heads;
+  return pa_decode_sm100(&q, stream);
 }
 
 int pa_merge_triples_sm100(void* out, int64_t out_stride_row, const float* m, const float* l,
