@@ -23,6 +23,17 @@ constexpr unsigned kFullMask = 0xffffffffu;
 constexpr uint32_t kSpinPolls = 1u << 15;
 constexpr uint32_t kWaitPollLimit = 1u << 22;
 
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may
+// start while its predecessor still runs; it must call grid_dependency_wait() before touching
+// the predecessor's results.  The predecessor calls grid_launch_dependents() once it no longer
+// minds sharing the SMs.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

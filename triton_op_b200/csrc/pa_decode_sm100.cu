@@ -327,8 +327,21 @@ int launch_reduce(const PaDecodeParams* p, float* tri_m, float* tri_l, float* tr
   if (rows == 0) return PA_OK;
   const int64_t blocks = (rows + 3) / 4;
   if (blocks > 0x7fffffff) return PA_ERR_TOO_LARGE;
-  pa::pa_reduce_kernel<<<(unsigned)blocks, 128, 0, stream>>>(r);
-  cudaError_t e = cudaGetLastError();
+  // Programmatic dependent launch: the reduce grid may be scheduled while the partition kernel
+  // drains; it waits (griddepcontrol.wait) before it reads anything that kernel wrote.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, pa::pa_reduce_kernel, r);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return PA_OK;
 }

@@ -166,6 +166,7 @@ pa_partition_fp8_p16_kernel(const __grid_constant__ KernelParams p) {
     fence_proxy_async();
   }
   const int n_sp = build_partition_index(p, seq_off, seq_ctx, scan_scratch);  // has __syncthreads
+  grid_launch_dependents();  // the reduce kernel may become resident; it waits for this grid to finish
   const int n_items = n_sp * p.Hkv;
   const int wtot = gridDim.x * NW;
   const int k_first = blockIdx.x * NW + warp;

@@ -245,6 +245,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p) {
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
+  grid_launch_dependents();  // the reduce kernel may become resident; it waits for this grid to finish
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + kOffTmemPtr);
   const uint32_t tmem_s = tmem_base;            // S^T of group g at column 32*g (+16 for tg = 1)
   const uint32_t tmem_o = tmem_base + kTmemO;   // O^T of group g, parity b at column 32*g + 16*b

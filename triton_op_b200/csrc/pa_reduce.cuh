@@ -48,33 +48,59 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(const __grid_constant__ 
   const int64_t tmp_base = (int64_t)seq * p.tmp_stride_seq + (int64_t)head * p.tmp_stride_head +
                            (int64_t)r * p.tmp_stride_row + 4 * lane;
 
-  float M = -INFINITY;
-  for (int i = lane; i < np; i += 32) M = fmaxf(M, p.max_logits[ws_base + (int64_t)i * p.ws_stride_part]);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(kFullMask, M, o));
+  // The launch may overlap the tail of the partition kernel (programmatic dependent launch):
+  // nothing that kernel wrote is read before this point.
+  grid_dependency_wait();
 
+  // Partitions are taken 32 at a time (lane = partition for the max / weight, then eight
+  // partial-output rows in flight per step) with a running maximum, so the whole row costs
+  // about one global-memory round trip for the usual np <= 32.
+  float M = -INFINITY;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   float W = 0.f;
   for (int p0 = 0; p0 < np; p0 += 32) {
     const int pi = p0 + lane;
-    float w = 0.f;
-    if (pi < np) {
-      const float m = p.max_logits[ws_base + (int64_t)pi * p.ws_stride_part];
-      const float l = p.exp_sums[ws_base + (int64_t)pi * p.ws_stride_part];
-      if (l > 0.f && m > -INFINITY) w = l * expf(m - M);
-    }
     const int cnt = min(32, np - p0);
-#pragma unroll 4
-    for (int j = 0; j < cnt; ++j) {
-      const float wj = __shfl_sync(kFullMask, w, j);
-      const uint2 raw = *reinterpret_cast<const uint2*>(
-          p.tmp_out + 2 * (tmp_base + (int64_t)(p0 + j) * p.tmp_stride_part));
-      W += wj;
-      if (wj != 0.f) {  // a zero-weight partition may hold anything
-        acc[0] = fmaf(wj, bf16_lo_to_f32(raw.x), acc[0]);
-        acc[1] = fmaf(wj, bf16_hi_to_f32(raw.x), acc[1]);
-        acc[2] = fmaf(wj, bf16_lo_to_f32(raw.y), acc[2]);
-        acc[3] = fmaf(wj, bf16_hi_to_f32(raw.y), acc[3]);
+    float m = -INFINITY, l = 0.f;
+    if (pi < np) {
+      m = p.max_logits[ws_base + (int64_t)pi * p.ws_stride_part];
+      l = p.exp_sums[ws_base + (int64_t)pi * p.ws_stride_part];
+    }
+    uint2 raw[8];  // first eight rows of the chunk are requested before the maximum is known
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      raw[j] = j < cnt ? *reinterpret_cast<const uint2*>(p.tmp_out + 2 * (tmp_base + (int64_t)(p0 + j) * p.tmp_stride_part))
+                       : make_uint2(0u, 0u);
+    float cm = (l > 0.f) ? m : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(kFullMask, cm, o));
+    const float newM = fmaxf(M, cm);
+    if (newM > M) {  // rescale what has been accumulated so far (M = -inf: nothing yet)
+      const float f = (M == -INFINITY) ? 0.f : expf(M - newM);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] *= f;
+      W *= f;
+      M = newM;
+    }
+    const float w = (l > 0.f && m > -INFINITY) ? l * expf(m - M) : 0.f;
+    for (int j0 = 0; j0 < cnt; j0 += 8) {
+      if (j0 > 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          raw[j] = (j0 + j) < cnt
+                       ? *reinterpret_cast<const uint2*>(p.tmp_out + 2 * (tmp_base + (int64_t)(p0 + j0 + j) * p.tmp_stride_part))
+                       : make_uint2(0u, 0u);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float wj = __shfl_sync(kFullMask, w, (j0 + j) & 31);
+        if ((j0 + j) < cnt && wj != 0.f) {  // a zero-weight partition may hold anything
+          W += wj;
+          acc[0] = fmaf(wj, bf16_lo_to_f32(raw[j].x), acc[0]);
+          acc[1] = fmaf(wj, bf16_hi_to_f32(raw[j].x), acc[1]);
+          acc[2] = fmaf(wj, bf16_lo_to_f32(raw[j].y), acc[2]);
+          acc[3] = fmaf(wj, bf16_hi_to_f32(raw[j].y), acc[3]);
+        }
       }
     }
   }
