@@ -1,6 +1,7 @@
 // Host side of the C ABI declared in include/pa_decode_sm100.h: argument validation, the
 // shared-memory carve and grid of the partition kernel, and the launches.  Nothing here
 // allocates device memory, synchronises or touches any stream but the caller's.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string.h>
@@ -50,15 +51,55 @@ int device_info(DeviceInfo** out) {
   return PA_OK;
 }
 
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link libcuda.
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+TensorMapEncodeFn tensor_map_encoder() {
+  static TensorMapEncodeFn fn = []() -> TensorMapEncodeFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult st;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &st) != cudaSuccess ||
+        st != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<TensorMapEncodeFn>(ptr);
+  }();
+  return fn;
+}
+
+// Descriptor of the value cache [NB, Hkv, 128, bs] (e4m3) for boxes of [128 head dims][span tokens],
+// written to shared memory with the swizzle the tensor core reads.
+int encode_value_map(const PaDecodeParams* p, CUtensorMap* out) {
+  TensorMapEncodeFn enc = tensor_map_encoder();
+  if (!enc) return PA_ERR_CUDA;
+  const cuuint32_t span = p->block_size == 64 ? 64 : 128;
+  const cuuint64_t dims[4] = {(cuuint64_t)p->block_size, (cuuint64_t)pa::kD, (cuuint64_t)p->num_kv_heads,
+                              (cuuint64_t)p->num_blocks};
+  const cuuint64_t strides[3] = {(cuuint64_t)p->block_size, (cuuint64_t)p->v_stride_head, (cuuint64_t)p->v_stride_block};
+  const cuuint32_t box[4] = {span, (cuuint32_t)pa::kD, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(p->value_cache), dims, strides, box,
+                         estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         span == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda_error = (int)r;
+    return PA_ERR_CUDA;
+  }
+  return PA_OK;
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int round_up(int v, int a) { return (v + a - 1) / a * a; }
 
 struct LaunchPlan {
   pa::KernelParams kp;
+  CUtensorMap vmap;   // tiled-copy descriptor of the value cache (pages of 64 tokens or more)
   int warps = 0;      // consumer warps per CTA
   int mtiles = 0;     // 8-row query tiles per warp
   bool per_token = false;
   bool tensor_path = false;  // tcgen05 kernel (else the mma.sync kernel)
+  int rows = 0;              // query rows per work item (tcgen05 kernel)
   int grid = 0;
   int smem = 0;
 };
@@ -102,12 +143,18 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
 
   const int eqG = p->query_group_size * p->query_len;
   if (p->kv_dtype != PA_DT_E4M3FN || p->q_dtype != PA_DT_BF16) return PA_ERR_UNSUPPORTED;
-  if (p->block_size != 16) return PA_ERR_UNSUPPORTED;
+  if (p->block_size != 16 && p->block_size != 64 && p->block_size != 1024) return PA_ERR_UNSUPPORTED;
   if (p->v_layout != PA_V_NORMAL) return PA_ERR_UNSUPPORTED;
   if (p->alibi_slopes) return PA_ERR_UNSUPPORTED;
-  if (eqG > 16) return PA_ERR_UNSUPPORTED;
-  if (p->partition_size % pa::kStageTokens != 0 || p->partition_size / p->block_size > 32)
-    return PA_ERR_UNSUPPORTED;
+  if (eqG > 64) return PA_ERR_UNSUPPORTED;
+  // tcgen05 kernel: 256-token partitions.  tune_warps == 4 / 8 explicitly asks for the mma.sync
+  // kernel, which also covers other partition sizes for 16-token pages and up to 16 query rows.
+  const bool tensor_path = p->partition_size == pa::tc::kItemTokens && p->tune_warps == 0;
+  if (!tensor_path) {
+    if (p->block_size != 16 || eqG > 16) return PA_ERR_UNSUPPORTED;
+    if (p->partition_size % pa::kStageTokens != 0 || p->partition_size / p->block_size > 32)
+      return PA_ERR_UNSUPPORTED;
+  }
   // bulk copies: 16-byte aligned sources, contiguous page-of-one-head runs
   if (!aligned16(p->key_cache) || !aligned16(p->value_cache) || !aligned16(p->query))
     return PA_ERR_ALIGNMENT;
@@ -180,35 +227,46 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   const int64_t items_cap = (int64_t)p->num_seqs * p->num_kv_heads * parts_cap;
   const int index_bytes = round_up((p->num_seqs + 1) * 4, 16) + round_up(p->num_seqs * 4 + 4, 16);
 
-  // tcgen05 kernel: 256-token partitions, up to 8 query rows per kv head.  tune_warps == 4 / 8
-  // explicitly asks for the mma.sync kernel (kept for the shapes the tensor path does not cover).
-  plan->tensor_path = p->partition_size == pa::tc::kItemTokens && eqG <= 8 && p->tune_warps == 0;
+  plan->tensor_path = tensor_path;
+  memset(&plan->vmap, 0, sizeof(plan->vmap));
   if (plan->tensor_path) {
+    if (p->block_size >= 64) {
+      rc = encode_value_map(p, &plan->vmap);
+      if (rc != PA_OK) return rc;
+    }
+    const int qr = eqG <= 4 ? 4 : (eqG <= 8 ? 8 : 16);   // query rows per work item
+    const int nrb = (eqG + qr - 1) / qr;                  // row blocks per (partition, head)
+    plan->rows = qr;
+    k.num_row_blocks = nrb;
     plan->warps = pa::tc::kThreads / 32;
     int off = pa::tc::kHeadBytes;
     k.off_seq_offsets = off;
     k.off_seq_ctx = off + round_up((p->num_seqs + 1) * 4, 16);
     off = round_up(off + index_bytes, 128);
     k.off_q = off;
-    // The ring must be deeper than the distance by which P.V trails QK^T in the issue loop: the
-    // barrier waits of the pipeline are only valid under that condition.
-    constexpr int kMinSlots = pa::tc::kNG;
-    int slots = pa::tc::kMaxSlots;
-    if (p->tune_stages >= kMinSlots && p->tune_stages < slots) slots = p->tune_stages;
-    const int qslot = pa::tc::q_slot_bytes(per_token);
-    for (; slots >= kMinSlots; --slots) {
-      const int off_p = round_up(off + slots * qslot, 128);
-      const int ring = round_up(off_p + pa::tc::kNG * pa::tc::kPTileBytes, 1024);
-      if (ring + slots * pa::tc::kSlotBytes <= dev->max_smem_optin) {
+    const int qslot = pa::tc::q_slot_bytes(qr, per_token);
+    // ring depths (K and query ring, V ring), deepest that fits
+    static const int kDepths[][2] = {{4, 4}, {4, 3}, {3, 3}, {3, 2}, {2, 2}, {2, 1}};
+    bool placed = false;
+    for (const auto& d : kDepths) {
+      if (p->tune_stages > 0 && d[0] > p->tune_stages && d[0] > 2) continue;
+      const int off_p = round_up(off + d[0] * qslot, 128);
+      const int ring = round_up(off_p + pa::tc::kNG * pa::tc::p_tile_bytes(qr), 1024);
+      const int total = ring + (d[0] + d[1]) * pa::tc::kHalfSlot;
+      if (total <= dev->max_smem_optin) {
         k.off_p = off_p;
         k.off_ring = ring;
+        k.off_vring = ring + d[0] * pa::tc::kHalfSlot;
+        k.num_stages = d[0];
+        k.num_vstages = d[1];
+        plan->smem = total;
+        placed = true;
         break;
       }
     }
-    if (slots < kMinSlots) return PA_ERR_TOO_LARGE;  // num_seqs too large for the in-kernel index
-    k.num_stages = slots;
-    plan->smem = k.off_ring + slots * pa::tc::kSlotBytes;
-    int64_t grid = items_cap < dev->sm_count ? items_cap : dev->sm_count;
+    if (!placed) return PA_ERR_TOO_LARGE;  // num_seqs too large for the in-kernel index
+    int64_t items = items_cap * nrb;
+    int64_t grid = items < dev->sm_count ? items : dev->sm_count;
     if (p->tune_ctas > 0 && p->tune_ctas < grid) grid = p->tune_ctas;
     plan->grid = grid < 1 ? 1 : (int)grid;
     return PA_OK;
@@ -259,27 +317,38 @@ int launch_partition_t(const LaunchPlan& plan, cudaStream_t stream) {
   return PA_OK;
 }
 
-template <bool PT, bool TRACE, int QR>
+template <int BS, int QR, bool PT, bool TRACE>
 int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
-  auto kern = pa::tc::pa_partition_fp8_tc_kernel<PT, TRACE, QR>;
+  auto kern = pa::tc::pa_partition_fp8_tc_kernel<BS, QR, PT, TRACE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
   if (e != cudaSuccess) return cuda_fail(e);
-  kern<<<plan.grid, pa::tc::kThreads, plan.smem, stream>>>(plan.kp);
+  kern<<<plan.grid, pa::tc::kThreads, plan.smem, stream>>>(plan.kp, plan.vmap);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return PA_OK;
 }
 
+template <int BS, bool TRACE>
+int launch_tensor_bs(const LaunchPlan& plan, cudaStream_t stream) {
+  const bool pt = plan.per_token;
+  switch (plan.rows) {
+    case 4: return pt ? launch_tensor_t<BS, 4, true, TRACE>(plan, stream) : launch_tensor_t<BS, 4, false, TRACE>(plan, stream);
+    case 8: return pt ? launch_tensor_t<BS, 8, true, TRACE>(plan, stream) : launch_tensor_t<BS, 8, false, TRACE>(plan, stream);
+    case 16: return pt ? launch_tensor_t<BS, 16, true, TRACE>(plan, stream) : launch_tensor_t<BS, 16, false, TRACE>(plan, stream);
+    default: return PA_ERR_UNSUPPORTED;
+  }
+}
+
 int launch_partition(const LaunchPlan& plan, cudaStream_t stream) {
   if (plan.kp.S == 0) return PA_OK;
   if (plan.tensor_path) {
-    const bool r4 = plan.kp.eqG <= 4;  // the softmax handles 4 query rows instead of 8
-    if (plan.kp.trace != nullptr) {  // tuning build of the kernel with the clock stamps compiled in
-      if (plan.per_token) return r4 ? launch_tensor_t<true, true, 4>(plan, stream) : launch_tensor_t<true, true, 8>(plan, stream);
-      return r4 ? launch_tensor_t<false, true, 4>(plan, stream) : launch_tensor_t<false, true, 8>(plan, stream);
+    switch (plan.kp.block_size) {
+      case 16:  // the tuning build (clock stamps compiled in) exists for this page size only
+        return plan.kp.trace != nullptr ? launch_tensor_bs<16, true>(plan, stream) : launch_tensor_bs<16, false>(plan, stream);
+      case 64: return launch_tensor_bs<64, false>(plan, stream);
+      case 1024: return launch_tensor_bs<1024, false>(plan, stream);
+      default: return PA_ERR_UNSUPPORTED;
     }
-    if (plan.per_token) return r4 ? launch_tensor_t<true, false, 4>(plan, stream) : launch_tensor_t<true, false, 8>(plan, stream);
-    return r4 ? launch_tensor_t<false, false, 4>(plan, stream) : launch_tensor_t<false, false, 8>(plan, stream);
   }
 #define PA_CASE(NW, MT, PT) \
   if (plan.warps == NW && plan.mtiles == MT && plan.per_token == PT) return launch_partition_t<NW, MT, PT>(plan, stream);

@@ -50,7 +50,10 @@ struct KernelParams {
   int32_t off_seq_ctx;         // int32[S]: clamped context lengths
   int32_t off_q;               // query staging (ring of tiles)
   int32_t off_p;               // probability tiles (tcgen05 kernel)
-  int32_t off_ring;            // per-warp stage ring
+  int32_t off_ring;            // stage ring (mma.sync kernel) / K ring (tcgen05 kernel)
+  int32_t off_vring;           // V ring (tcgen05 kernel)
+  int32_t num_vstages;         // V ring depth (tcgen05 kernel)
+  int32_t num_row_blocks;      // ceil(eqG / rows per work item) (tcgen05 kernel)
 };
 
 // Fixed head of the shared-memory carve: mbarriers and the scan scratch.

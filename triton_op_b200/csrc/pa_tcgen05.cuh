@@ -23,6 +23,27 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
          ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
 }
 
+// Swizzled K-major operand (what a tiled TMA copy with CU_TENSOR_MAP_SWIZZLE_{64,128}B writes):
+// rows are `span` bytes apart (span = 64 or 128), the 16-byte chunks of a row are XOR-ed with
+// the row number inside each group of 8 rows, groups are 8 * span bytes apart.  The tile base
+// is aligned to 8 * span.  layout code: 4 = 64-byte swizzle, 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc_swizzled(uint32_t addr, uint32_t span) {
+  const uint64_t layout = span == 128 ? 2ull : 4ull;
+  return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(((8 * span) >> 4) & 0x3fffu) << 32) |
+         (1ull << 46) | (layout << 61);
+}
+
+// Tiled TMA load of one 4-D box into this CTA's shared memory (no multicast), completion
+// counted on `bar`.  c0 is the innermost coordinate and must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2, int c3,
+                                            uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3, %4, %5}], [%6], %7;" ::"r"(dst),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar), "l"(policy)
+      : "memory");
+}
+
 // ---- instruction descriptor (upper 32 bits of the "idesc" operand) ----------------------------
 //   bits [4,6)  accumulator format (1 = f32)      bits [7,10) A format     bits [10,13) B format
 //   bit 15 / 16 A / B major (0 = K-major)          bits [17,23) N >> 3      bits [24,29) M >> 4
