@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "../../include/pa_decode_sm100.h"
+#include "pa_partition_bf16.cuh"
 #include "pa_partition_fp8.cuh"
 #include "pa_partition_tc.cuh"
 #include "pa_reduce.cuh"
@@ -99,6 +100,7 @@ struct LaunchPlan {
   int mtiles = 0;     // 8-row query tiles per warp
   bool per_token = false;
   bool tensor_path = false;  // tcgen05 kernel (else the mma.sync kernel)
+  bool bf16_kv = false;      // bf16 KV cache (mma.sync bf16 kernel)
   int rows = 0;              // query rows per work item (tcgen05 kernel)
   int grid = 0;
   int smem = 0;
@@ -142,24 +144,29 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   if (rc != PA_OK) return rc;
 
   const int eqG = p->query_group_size * p->query_len;
-  if (p->kv_dtype != PA_DT_E4M3FN || p->q_dtype != PA_DT_BF16) return PA_ERR_UNSUPPORTED;
+  if (p->q_dtype != PA_DT_BF16) return PA_ERR_UNSUPPORTED;
+  if (p->kv_dtype != PA_DT_E4M3FN && p->kv_dtype != PA_DT_BF16) return PA_ERR_UNSUPPORTED;
+  const bool bf16_kv = p->kv_dtype == PA_DT_BF16;
+  const int kv_item = bf16_kv ? 2 : 1;  // bytes per cache element
+  if (bf16_kv && p->kv_quant_mode == PA_QUANT_PER_TOKEN) return PA_ERR_UNSUPPORTED;
   if (p->block_size != 16 && p->block_size != 64 && p->block_size != 1024) return PA_ERR_UNSUPPORTED;
   if (p->v_layout != PA_V_NORMAL) return PA_ERR_UNSUPPORTED;
   if (p->alibi_slopes) return PA_ERR_UNSUPPORTED;
   if (eqG > 64) return PA_ERR_UNSUPPORTED;
   // tcgen05 kernel: 256-token partitions.  tune_warps == 4 / 8 explicitly asks for the mma.sync
   // kernel, which also covers other partition sizes for 16-token pages and up to 16 query rows.
-  const bool tensor_path = p->partition_size == pa::tc::kItemTokens && p->tune_warps == 0;
+  const bool tensor_path = !bf16_kv && p->partition_size == pa::tc::kItemTokens && p->tune_warps == 0;
   if (!tensor_path) {
     if (p->block_size != 16 || eqG > 16) return PA_ERR_UNSUPPORTED;
-    if (p->partition_size % pa::kStageTokens != 0 || p->partition_size / p->block_size > 32)
+    if (p->partition_size % (bf16_kv ? pa::kPageTokens : pa::kStageTokens) != 0 ||
+        p->partition_size / p->block_size > 32)
       return PA_ERR_UNSUPPORTED;
   }
   // bulk copies: 16-byte aligned sources, contiguous page-of-one-head runs
   if (!aligned16(p->key_cache) || !aligned16(p->value_cache) || !aligned16(p->query))
     return PA_ERR_ALIGNMENT;
-  if ((p->k_stride_block & 15) || (p->k_stride_head & 15) || (p->v_stride_block & 15) ||
-      (p->v_stride_head & 15))
+  if (((p->k_stride_block * kv_item) & 15) || ((p->k_stride_head * kv_item) & 15) ||
+      ((p->v_stride_block * kv_item) & 15) || ((p->v_stride_head * kv_item) & 15))
     return PA_ERR_ALIGNMENT;
   if (p->q_stride_head != pa::kD || (p->q_stride_seq & 7)) return PA_ERR_ALIGNMENT;
   const bool per_token = p->kv_quant_mode == PA_QUANT_PER_TOKEN;
@@ -199,10 +206,10 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   k.ctx_cap = cap > 0x7fffffff ? 0x7fffffff : (int32_t)cap;
   k.q_stride_seq = p->q_stride_seq * 2;    // bf16 -> bytes
   k.q_stride_head = p->q_stride_head * 2;
-  k.k_stride_block = p->k_stride_block;    // e4m3: elements are bytes
-  k.k_stride_head = p->k_stride_head;
-  k.v_stride_block = p->v_stride_block;
-  k.v_stride_head = p->v_stride_head;
+  k.k_stride_block = p->k_stride_block * kv_item;   // elements -> bytes
+  k.k_stride_head = p->k_stride_head * kv_item;
+  k.v_stride_block = p->v_stride_block * kv_item;
+  k.v_stride_head = p->v_stride_head * kv_item;
   k.bt_stride_seq = p->bt_stride_seq;
   k.q_scale_stride_seq = p->q_scale_stride_seq;
   k.kvs_stride_block = p->kv_scale_stride_block;
@@ -272,12 +279,14 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
     return PA_OK;
   }
 
+  plan->bf16_kv = bf16_kv;
   plan->warps = p->tune_warps > 0 ? p->tune_warps : 8;
   if (plan->warps != 4 && plan->warps != 8) return PA_ERR_UNSUPPORTED;
+  if (bf16_kv) plan->warps = 8;
 
   // shared-memory carve
-  const int stage = pa::stage_bytes(per_token);
-  const int qbuf = plan->mtiles * 8 * pa::kQRowBytes;
+  const int stage = bf16_kv ? pa::kBf16Stage : pa::stage_bytes(per_token);
+  const int qbuf = bf16_kv ? pa::kBf16QBuf : plan->mtiles * 8 * pa::kQRowBytes;
   int off = pa::kSmemHeadBytes;
   k.off_seq_offsets = off;
   off += round_up((p->num_seqs + 1) * 4, 16);
@@ -349,6 +358,14 @@ int launch_partition(const LaunchPlan& plan, cudaStream_t stream) {
       case 1024: return launch_tensor_bs<1024, false>(plan, stream);
       default: return PA_ERR_UNSUPPORTED;
     }
+  }
+  if (plan.bf16_kv) {
+    auto kern = pa::pa_partition_bf16_p16_kernel<8>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
+    if (e != cudaSuccess) return cuda_fail(e);
+    kern<<<plan.grid, 8 * 32, plan.smem, stream>>>(plan.kp);
+    e = cudaGetLastError();
+    return e != cudaSuccess ? cuda_fail(e) : PA_OK;
   }
 #define PA_CASE(NW, MT, PT) \
   if (plan.warps == NW && plan.mtiles == MT && plan.per_token == PT) return launch_partition_t<NW, MT, PT>(plan, stream);

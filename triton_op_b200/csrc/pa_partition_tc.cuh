@@ -740,10 +740,11 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       }
 
       // ---- pass 2: P = exp2(s - m) * 256, split into hi / lo e4m3, stored as P^T
+      float psum_all[NCH][RC];
 #pragma unroll
       for (int ch = 0; ch < NCH; ++ch) {
         if (NCH > 1) logits(ch, s_keep);  // recomputed rather than kept: registers
-        float psum[RC];
+        float (&psum)[RC] = psum_all[ch];
         uint32_t pbytes[2][2 * ((RC + 3) / 4)];  // [tg][hi words, lo words], row q = byte q % 4
         float hi[2][RC], lo[2][RC];
 #pragma unroll
@@ -773,14 +774,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
             sts8(p_at[tg] + (nh >> 3) * kPSbo + (nh & 7) * 16, pbytes[tg][q >> 2] >> (8 * (q & 3)));
             sts8(p_at[tg] + (nl >> 3) * kPSbo + (nl & 7) * 16, pbytes[tg][W + (q >> 2)] >> (8 * (q & 3)));
           }
-        }
-        // row sums, needed only by the epilogue of this item
-        if constexpr (RC == 8) {
-          const float wsum = warp_sum8(psum, lane);
-          if ((lane & 3) == 0) red_sum[par * 64 + (ch * 8 + ((lane >> 2) & 7)) * 4 + wq] = wsum;
-        } else {
-          const float wsum = warp_sum4(psum, lane);
-          if ((lane & 7) == 0) red_sum[par * 64 + ((lane >> 3) & 3) * 4 + wq] = wsum;
         }
       }
       if (PER_TOKEN && r == 0) v_norm[par] = vnorm;
@@ -821,6 +814,17 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarPFull, grp));
       if (wq == 0) stamp(4, i, 2);
+      // row sums, needed only by the epilogue of this item: off the path to P.V
+#pragma unroll
+      for (int ch = 0; ch < NCH; ++ch) {
+        if constexpr (RC == 8) {
+          const float wsum = warp_sum8(psum_all[ch], lane);
+          if ((lane & 3) == 0) red_sum[par * 64 + (ch * 8 + ((lane >> 2) & 7)) * 4 + wq] = wsum;
+        } else {
+          const float wsum = warp_sum4(psum_all[ch], lane);
+          if ((lane & 7) == 0) red_sum[par * 64 + ((lane >> 3) & 3) * 4 + wq] = wsum;
+        }
+      }
       return true;
     };
 
