@@ -178,3 +178,42 @@ def test_llama8b_shape_full_size_against_oracle_on_device():
     out1, _ = run_operator(inp)
     expect = 1.5 * float(inp.value_scale)
     assert torch.allclose(out1.float(), torch.full_like(out1.float(), expect), rtol=1e-2, atol=0)
+
+
+# ----------------------------------------------------------------------------- reference test matrix
+# test_pa_mtp.py:48-54 of the reference: block sizes {16, 64, 1024}, (Hq, Hkv) in {(5,1), (8,1),
+# (10,1), (16,1), (64,4)}, query length 1-4, context {512, 4096, 4097}; here at batch 3, uniform
+# data as in that harness, per-token scales (what the harness feeds the Gluon kernel), with the
+# oracle run on the GPU.
+_MATRIX = [(bs, hq, hkv, ql, ctx)
+           for bs in (16, 64, 1024)
+           for (hq, hkv) in ((5, 1), (8, 1), (10, 1), (16, 1), (64, 4))
+           for ql in (1, 2, 3, 4)
+           for ctx in (512, 4097)]
+
+
+@pytest.mark.parametrize("bs,hq,hkv,ql,ctx", _MATRIX)
+def test_reference_matrix(bs, hq, hkv, ql, ctx):
+    from triton_op_b200.inputs import DecodeConfig, make_inputs
+    cfg = DecodeConfig(f"m{bs}_{hq}_{hkv}_{ql}_{ctx}", 3, hq, hkv, bs, ql, ("fixed", ctx), quant="per_token")
+    inp = make_inputs(cfg, seed=bs + hq + ql, device=DEV, dist="uniform")
+    st = _status()
+    out, _ = run_operator(inp, status=st)
+    ref = oracle_output(inp)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert_close(out, ref, what=cfg.name)
+
+
+@pytest.mark.parametrize("name,num_seqs", [("cfg3_llama70b_mtp", 12), ("cfg4_longctx", 3), ("cfg5_serving_fp8", 48),
+                                           ("cfg5_serving_bf16", 48)])
+def test_baseline_configs_reduced_batch(name, num_seqs):
+    """The other benchmark configurations at their real shapes and length distributions, fewer sequences."""
+    from triton_op_b200.inputs import CONFIGS, make_inputs
+    inp = make_inputs(CONFIGS[name], seed=1, device=DEV, num_seqs=num_seqs)
+    st = _status()
+    out, _ = run_operator(inp, status=st)
+    ref = oracle_output(inp)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert_close(out, ref, what=name)
