@@ -216,6 +216,8 @@ def run_ours(args, rank: int, world: int, local: int):
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
     cfg = CONFIGS[args.workload]
+    if args.num_seqs > 0:   # reduced batch: for profiler captures, never for a reported number
+        cfg = type(cfg)(**{**cfg.__dict__, "num_seqs": args.num_seqs, "pool_blocks": None})
     inp = make_inputs(cfg, seed=rank, device=dev)          # every rank its own batch (weak scaling)
     c = inp.cfg
     out = torch.empty_like(inp.query)
@@ -317,16 +319,18 @@ def run_ours(args, rank: int, world: int, local: int):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "us_per_call": ms_step * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 x e4m3 -> f32",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 x bf16 -> f32" if c.kv_dtype == "bf16" else "e4m3 x e4m3 -> f32",
         "data": "synthetic",
         "pct_of_nominal_hbm": 100.0 * value / (NOMINAL_HBM_GBS * world),
         "config": {"workload": args.workload, "num_seqs_per_gpu": c.num_seqs, "q_heads": c.q_heads,
                    "kv_heads": c.kv_heads, "head_size": c.head_size, "block_size": c.block_size,
-                   "query_len": c.query_len, "context_len": inp.max_context, "kv": "fp8 e4m3fn, per-tensor scales",
+                   "query_len": c.query_len, "context_len": inp.max_context if c.context[0] == "fixed" else str(c.context),
+                   "kv": ("bf16" if c.kv_dtype == "bf16" else "fp8 e4m3fn") + ", " + c.quant.replace("_", "-") + " scales",
                    "partition_size": c.partition_size, "kv_bytes_per_gpu": kv_bytes,
                    "l2": "inputs larger than L2 (KV read per step: %.0f MB per GPU)" % (kv_bytes / 1e6),
                    "sharding": "sequences, no collective"},
-        "roofline": {"bound": "hbm", "kernel": "pa_partition_fp8_tc_kernel", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "partition kernel (pa_partition_sm100)", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind + " (torch copy_, read+write)", "unit": "GB/s", "frac": achieved / peak,
                      "us_per_launch": us_partition, "algorithmic_bytes": kv_bytes,
                      "traffic": (NCU_TRAFFIC_PER_KV_BYTE * kv_bytes) if NCU_TRAFFIC_PER_KV_BYTE else None},
@@ -350,6 +354,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2_llama8b", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--num-seqs", type=int, default=0,
+                    help="override the workload's batch size (profiler captures of the large workloads)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

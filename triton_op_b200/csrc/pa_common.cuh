@@ -69,13 +69,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
-// Bounded wait; false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait; false when the limit ran out.  The polling loop is one shared out-of-line
+// function: inlined at every wait site (and unrolled) it made up almost half of the kernel's
+// code, and the kernels' hot loops should stay inside the instruction cache.
+__device__ __noinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity) {
+#pragma unroll 1
   for (uint32_t it = 0; it < kWaitPollLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > kSpinPolls) __nanosleep(200);
   }
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_poll(bar, parity);
 }
 
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {

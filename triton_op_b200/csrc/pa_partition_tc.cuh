@@ -230,7 +230,7 @@ struct Geo {
   // start address (inside the V slot) of the operand of k-step ks (tokens [32*ks, 32*ks + 32))
   __host__ __device__ static constexpr int v_kstep(int ks) {
     if (BS == 16) return 2 * ks * 2048;
-    const int per_box = kVSpan / 32;                 // k-steps per box
+    const int per_box = kVSpan >= 32 ? kVSpan / 32 : 1;   // k-steps per box
     return (ks / per_box) * kVBox + (ks % per_box) * 32;
   }
   // token (0..255 inside the item) held by TMEM lane r of S^T tile tg
@@ -416,6 +416,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     // ------------------------------------------------------------------ query (+ scales) producer
     // lane -> row n0 = lane / 4 of a pass of 8 rows, quarter qq = lane % 4 of the head dims (32 each)
     constexpr int kPasses = QR > 8 ? QR / 8 : 1;
+    static_assert(kPasses <= 2, "the pass loop selects between two register sets");
     const int n0 = lane >> 2, qq = lane & 3;
     auto load_q = [&](const TcItem& it, uint4 (&raw)[kPasses][4]) {
 #pragma unroll
@@ -492,7 +493,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       stamp(2, i, 1);
       const uint32_t qt = q_ring + slot * kQSlotBytes;
       const uint32_t aux = qt + kQTile;
-#pragma unroll
+      // (rolled: the code of every role's loop should stay resident in the instruction cache)
+#pragma unroll 1
       for (int ps = 0; ps < kPasses; ++ps) {
         const int n = ps * 8 + n0;
         const int row = it.rb * QR + n;
@@ -500,7 +502,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         float x[32];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const uint32_t w[4] = {qraw[ps][e].x, qraw[ps][e].y, qraw[ps][e].z, qraw[ps][e].w};
+          uint4 qv = qraw[0][e];
+          if (kPasses > 1 && ps == 1) qv = qraw[kPasses - 1][e];
+          const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             x[e * 8 + 2 * k] = bf16_lo_to_f32(w[k]);
@@ -659,19 +663,24 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       // orders the producer's scale writes before the reads below.
       if (!wait(bar(kBarKQFull, slot), use & 1)) return false;
       const uint32_t aux = q_ring + slot * kQSlotBytes + kQTile;
-      float row_scale[QR];
-      int lim[QR];  // row q sees token j iff j < ctx - lim[q]; negative: padding row, sees nothing
+      // per-row constants of one chunk of rows; with several chunks they are fetched again for
+      // every chunk (the chunk loops are rolled), so the query slot is released after pass 2
+      float row_scale[RC];
+      int lim[RC];  // row q sees token j iff j < ctx - lim[q]; negative: padding row, sees nothing
+      auto load_row_consts = [&](int ch) {
 #pragma unroll
-      for (int q4 = 0; q4 < QR; q4 += 4) {
-        const uint4 a = lds128(aux + q4 * 4);
-        const uint4 b = lds128(smem_addr(row_lim) + (it.rb * QR + q4) * 4);
-        const uint32_t w[4] = {a.x, a.y, a.z, a.w}, li[4] = {b.x, b.y, b.z, b.w};
+        for (int q4 = 0; q4 < RC; q4 += 4) {
+          const uint4 a = lds128(aux + (ch * RC + q4) * 4);
+          const uint4 b = lds128(smem_addr(row_lim) + (it.rb * QR + ch * RC + q4) * 4);
+          const uint32_t w[4] = {a.x, a.y, a.z, a.w}, li[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          row_scale[q4 + e] = __uint_as_float(w[e]) * base_scale;
-          lim[q4 + e] = (int)li[e];
+          for (int e = 0; e < 4; ++e) {
+            row_scale[q4 + e] = __uint_as_float(w[e]) * base_scale;
+            lim[q4 + e] = (int)li[e];
+          }
         }
-      }
+      };
+      if (NCH == 1) load_row_consts(0);
       float ks_tok[2] = {1.f, 1.f}, vs_tok[2] = {1.f, 1.f};
       if (PER_TOKEN) {
 #pragma unroll
@@ -680,9 +689,12 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           vs_tok[tg] = __uint_as_float(lds32(aux + 64 + kItemTokens * 4 + tok[tg] * 4));
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarQEmpty, slot));
+      if (NCH == 1) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kBarQEmpty, slot));
+      }
       fence_after_sync();
+      if (wq == 0) stamp(6, i, 0);
 
       const int room[2] = {it.ctx - (it.tok0 + tok[0]), it.ctx - (it.tok0 + tok[1])};  // > lim <=> visible
       if (PER_TOKEN) {
@@ -694,22 +706,22 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         uint32_t h[2][8], l[2][8];
         load_rows(tmem_grp, ch, h[0], l[0]);
         load_rows(tmem_grp + N, ch, h[1], l[1]);
+        if (NCH > 1) load_row_consts(ch);
         tmem_ld_wait();
 #pragma unroll
         for (int tg = 0; tg < 2; ++tg) {
 #pragma unroll
           for (int q = 0; q < RC; ++q) {
-            const int row = ch * RC + q;
-            float v = row_value(h[tg], l[tg], q) * row_scale[row];
+            float v = row_value(h[tg], l[tg], q) * row_scale[q];
             if (PER_TOKEN) v *= ks_tok[tg];
-            s[tg][q] = (room[tg] > lim[row] && lim[row] >= 0) ? v : -INFINITY;
+            s[tg][q] = (room[tg] > lim[q] && lim[q] >= 0) ? v : -INFINITY;
           }
         }
       };
 
       // ---- pass 1: partition maximum per row (integer warp reduction on order-preserving keys)
       float s_keep[2][RC];
-#pragma unroll
+#pragma unroll 1
       for (int ch = 0; ch < NCH; ++ch) {
         logits(ch, s_keep);
         int key[RC];
@@ -725,6 +737,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         const int vk = __reduce_max_sync(kFullMask, float_to_ordered(fmaxf(vs_tok[0], vs_tok[1])));
         if (lane == 0) v_max[grp * 4 + wq] = ordered_to_float(vk);
       }
+      if (wq == 0) stamp(6, i, 1);
       named_barrier_sync(bar_a, 128);
       float vinv = 1.0f, vnorm = 1.0f;
       if (PER_TOKEN) {
@@ -739,12 +752,22 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (!wait(bar(kBarOFull, 2 * grp + (int)(pu & 1)), (pu >> 1) & 1)) return false;
       }
 
+      if (wq == 0) stamp(6, i, 2);
       // ---- pass 2: P = exp2(s - m) * 256, split into hi / lo e4m3, stored as P^T
-      float psum_all[NCH][RC];
-#pragma unroll
+      // row sums of one chunk: lane ends up with the sum of one row over the warp's 64 tokens
+      auto row_sums = [&](int ch, const float (&psum)[RC]) {
+        if constexpr (RC == 8) {
+          const float wsum = warp_sum8(psum, lane);
+          if ((lane & 3) == 0) red_sum[par * 64 + (ch * 8 + ((lane >> 2) & 7)) * 4 + wq] = wsum;
+        } else {
+          const float wsum = warp_sum4(psum, lane);
+          if ((lane & 7) == 0) red_sum[par * 64 + ((lane >> 3) & 3) * 4 + wq] = wsum;
+        }
+      };
+      float psum[RC];
+#pragma unroll 1
       for (int ch = 0; ch < NCH; ++ch) {
         if (NCH > 1) logits(ch, s_keep);  // recomputed rather than kept: registers
-        float (&psum)[RC] = psum_all[ch];
         uint32_t pbytes[2][2 * ((RC + 3) / 4)];  // [tg][hi words, lo words], row q = byte q % 4
         float hi[2][RC], lo[2][RC];
 #pragma unroll
@@ -761,6 +784,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           split_hi_lo(PER_TOKEN ? p1 * (vs_tok[1] * vinv) : p1, hi[1][q], lo[1][q]);
         }
         constexpr int W = (RC + 3) / 4;
+        // tile rows: hi half at row ch * RC + q, lo half at row QR + ch * RC + q
+        const uint32_t hi_at = RC == 8 ? ch * kPSbo : 0;
+        const uint32_t lo_at = RC == 8 ? (QR / 8 + ch) * kPSbo : QR * 16;
 #pragma unroll
         for (int tg = 0; tg < 2; ++tg) {
 #pragma unroll
@@ -770,13 +796,18 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           }
 #pragma unroll
           for (int q = 0; q < RC; ++q) {
-            const int nh = ch * RC + q, nl = QR + ch * RC + q;  // tile rows of the hi / lo half
-            sts8(p_at[tg] + (nh >> 3) * kPSbo + (nh & 7) * 16, pbytes[tg][q >> 2] >> (8 * (q & 3)));
-            sts8(p_at[tg] + (nl >> 3) * kPSbo + (nl & 7) * 16, pbytes[tg][W + (q >> 2)] >> (8 * (q & 3)));
+            sts8(p_at[tg] + hi_at + q * 16, pbytes[tg][q >> 2] >> (8 * (q & 3)));
+            sts8(p_at[tg] + lo_at + q * 16, pbytes[tg][W + (q >> 2)] >> (8 * (q & 3)));
           }
         }
+        if (NCH > 1) row_sums(ch, psum);
+      }
+      if (NCH > 1) {  // the query slot's scales were read until here
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kBarQEmpty, slot));
       }
       if (PER_TOKEN && r == 0) v_norm[par] = vnorm;
+      if (wq == 0) stamp(6, i, 3);
 
       // Bytes of V past the context (absent pages, tokens past the end of the last page) may
       // hold anything, NaN patterns included, and 0 * NaN would poison O^T: clear them.
@@ -815,16 +846,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       if (lane == 0) mbar_arrive(bar(kBarPFull, grp));
       if (wq == 0) stamp(4, i, 2);
       // row sums, needed only by the epilogue of this item: off the path to P.V
-#pragma unroll
-      for (int ch = 0; ch < NCH; ++ch) {
-        if constexpr (RC == 8) {
-          const float wsum = warp_sum8(psum_all[ch], lane);
-          if ((lane & 3) == 0) red_sum[par * 64 + (ch * 8 + ((lane >> 2) & 7)) * 4 + wq] = wsum;
-        } else {
-          const float wsum = warp_sum4(psum_all[ch], lane);
-          if ((lane & 7) == 0) red_sum[par * 64 + ((lane >> 3) & 3) * 4 + wq] = wsum;
-        }
-      }
+      if (NCH == 1) row_sums(0, psum);
       return true;
     };
 
@@ -840,18 +862,27 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       if (wq == 0) stamp(5, j, 1);
       fence_after_sync();
       const float vfin = PER_TOKEN ? v_norm[par] : v_scale_t;
-      const int64_t ws_base = (int64_t)it.seq * p.ws_stride_seq + (int64_t)it.head * p.ws_stride_head +
-                              (int64_t)it.part * p.ws_stride_part + it.rb * QR;
-      unsigned short* tmp = reinterpret_cast<unsigned short*>(p.tmp_out) + (int64_t)it.seq * p.tmp_stride_seq +
+      const int rows = min(QR, p.eqG - it.rb * QR);   // valid rows of this block
+      // thread `row` of the group stores the row's partition maximum and exponential sum
+      if (r < rows) {
+        const int64_t ws = (int64_t)it.seq * p.ws_stride_seq + (int64_t)it.head * p.ws_stride_head +
+                           (int64_t)it.part * p.ws_stride_part + it.rb * QR + r;
+        const float4 l4 = *reinterpret_cast<const float4*>(rs + r * 4);
+        p.max_logits[ws] = m_fin[par * 16 + r] * kLn2;
+        p.exp_sums[ws] = ((l4.x + l4.y) + (l4.z + l4.w)) * (1.0f / 256.0f);
+      }
+      // lane r holds head dim r of every row: 2-byte stores, 64 contiguous bytes per warp and row
+      unsigned short* dst = reinterpret_cast<unsigned short*>(p.tmp_out) + (int64_t)it.seq * p.tmp_stride_seq +
                             (int64_t)it.head * p.tmp_stride_head + (int64_t)it.part * p.tmp_stride_part +
                             (int64_t)(it.rb * QR) * p.tmp_stride_row + r;
-      const int rows = min(QR, p.eqG - it.rb * QR);   // valid rows of this block
+      const int64_t row_stride = p.tmp_stride_row;
       const uint32_t otile = tmem_grp + 2 * N + (int)(gu & 1) * N;
-#pragma unroll
+#pragma unroll 1
       for (int ch = 0; ch < NCH; ++ch) {
         uint32_t h[8], l[8];
         load_rows(otile, ch, h, l);
         tmem_ld_wait();
+        if (wq == 0) stamp(7, j, 2 * ch);
 #pragma unroll
         for (int q = 0; q < RC; ++q) {
           const int row = ch * RC + q;
@@ -859,14 +890,10 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           const float lsum = (l4.x + l4.y) + (l4.z + l4.w);   // in units of 1/256
           const float f = lsum > 0.f ? __fdividef(vfin, lsum) : 0.f;
           const float o = row_value(h, l, q) * f;
-          if (row < rows) {
-            tmp[(int64_t)row * p.tmp_stride_row] = (unsigned short)(pack_bf16x2(o, 0.f) & 0xffffu);
-            if (r == row) {
-              p.max_logits[ws_base + row] = m_fin[par * 16 + row] * kLn2;
-              p.exp_sums[ws_base + row] = lsum * (1.0f / 256.0f);
-            }
-          }
+          if (row < rows) *dst = (unsigned short)(pack_bf16x2(o, 0.f) & 0xffffu);
+          dst += row_stride;
         }
+        if (wq == 0) stamp(7, j, 2 * ch + 1);
       }
       fence_before_sync();  // the O^T loads are ordered before this warp's next arrival on the P barrier
       if (wq == 0) stamp(5, j, 2);
@@ -879,15 +906,20 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     if (grp < n_local) cur.init(first + grp * stride, NG * stride, p, seq_off);
     TcItem it_prev{};
     int prev = -1;
-    for (int i = grp; i < n_local && !dead; i += NG) {
-      const TcItem it = cur.item(p, seq_off, seq_ctx);
-      cur.advance(p, seq_off);
-      if (!softmax(i, it)) { fail(); break; }
-      if (prev >= 0 && !epilogue(prev, it_prev, false)) { fail(); break; }
+    // one call site each for softmax and epilogue: the code of this loop should stay small
+    for (int i = grp; !dead; i += NG) {
+      const bool more = i < n_local;
+      TcItem it{};
+      if (more) {
+        it = cur.item(p, seq_off, seq_ctx);
+        cur.advance(p, seq_off);
+        if (!softmax(i, it)) { fail(); break; }
+      }
+      if (prev >= 0 && !epilogue(prev, it_prev, !more)) { fail(); break; }
+      if (!more) break;
       it_prev = it;
       prev = i;
     }
-    if (!dead && prev >= 0 && !epilogue(prev, it_prev, true)) fail();
   }
 
   // ---------------------------------------------------------------------- teardown
