@@ -218,22 +218,55 @@ def run_ours(args, rank: int, world: int, local: int):
     cfg = CONFIGS[args.workload]
     if args.num_seqs > 0:   # reduced batch: for profiler captures, never for a reported number
         cfg = type(cfg)(**{**cfg.__dict__, "num_seqs": args.num_seqs, "pool_blocks": None})
-    inp = make_inputs(cfg, seed=rank, device=dev)          # every rank its own batch (weak scaling)
-    c = inp.cfg
-    out = torch.empty_like(inp.query)
+    mode = args.sharding
+    if mode == "auto":      # long single-head contexts split by KV partition, batches by sequence
+        mode = "kv-partitions" if (args.workload == "cfg4_longctx" and world > 1) else "sequences-weak"
     status = torch.zeros((), dtype=torch.int32, device=dev)
+    decoder = None
+    if mode == "sequences-weak":
+        inp = make_inputs(cfg, seed=rank, device=dev)      # every rank its own batch of the full size
+    elif mode == "sequences-strong":
+        # one global batch; every rank computes the same plan and builds only its own sequences
+        from triton_op_b200.inputs import draw_context_lens
+        from triton_op_b200.sharding import shard_sequences
+        gen = torch.Generator()
+        gen.manual_seed(0)
+        lens = draw_context_lens(cfg, gen)
+        policy = "balanced" if cfg.context[0] == "lognormal" else "contiguous"
+        mine = shard_sequences(lens.tolist(), world, policy)[rank]
+        sub = type(cfg)(**{**cfg.__dict__, "num_seqs": len(mine), "pool_blocks": None})
+        inp = make_inputs(sub, seed=rank, device=dev, context_lens=lens[mine])
+    else:
+        # every rank builds the same pool (same seed) and reads only the pages of its ranges
+        from triton_op_b200.sharding import KvShardedDecoder, plan_kv_shards
+        inp = make_inputs(cfg, seed=0, device=dev)
+        plan = plan_kv_shards(inp.context_lens.tolist(), world, cfg.partition_size, cfg.query_len)[rank]
+        decoder = KvShardedDecoder(inp.query, inp.key_cache, inp.value_cache, plan, inp.block_tables,
+                                   inp.softmax_scale, inp.key_scale, inp.value_scale,
+                                   partition_size=cfg.partition_size, status=status)
+    c = inp.cfg
+    out = torch.empty_like(inp.query) if decoder is None else decoder.out
 
     def call(query, ctx, bt):
+        if decoder is not None:       # KV-partition sharding: partial attention, all-gather, merge
+            if query is not decoder.query:
+                decoder.query.copy_(query, non_blocking=True)
+                decoder.context_lens.copy_(ctx, non_blocking=True)
+                decoder.tables.copy_(bt, non_blocking=True)
+            decoder.step()
+            return
         paged_attention_decode(out, query, inp.key_cache, inp.value_cache, ctx, bt, inp.softmax_scale,
                                c.query_len, inp.max_context, torch.bfloat16, None, inp.key_scale,
                                inp.value_scale, partition_size=c.partition_size, status=status)
 
-    kv_bytes = inp.kv_bytes
+    kv_bytes = inp.kv_bytes if decoder is None else decoder.kv_bytes
+    step_ctx = inp.context_lens if decoder is None else decoder.context_lens
+    step_bt = inp.block_tables if decoder is None else decoder.tables
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
     # ---- device-resident inputs: K steps between two events on the launching stream
     for _ in range(args.warmup):
-        call(inp.query, inp.context_lens, inp.block_tables)
+        call(inp.query, step_ctx, step_bt)
     torch.cuda.synchronize()
     barrier(world)
     sampler = ClockSampler(local)
@@ -243,16 +276,19 @@ def run_ours(args, rank: int, world: int, local: int):
     torch.cuda.synchronize()
     e0.record()
     for _ in range(args.steps):
-        call(inp.query, inp.context_lens, inp.block_tables)
+        call(inp.query, step_ctx, step_bt)
     e1.record()
     torch.cuda.synchronize()
     barrier(world)
     ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps, world, dev)
 
     # ---- the partition kernel alone (the dominant kernel) for the roofline
-    p, keep = build_params(out, inp.query, inp.key_cache, inp.value_cache, inp.context_lens, inp.block_tables,
-                           inp.softmax_scale, c.query_len, inp.max_context, torch.bfloat16, None,
-                           inp.key_scale, inp.value_scale, None, c.partition_size, None, None, None, status, None)
+    if decoder is None:
+        p, keep = build_params(out, inp.query, inp.key_cache, inp.value_cache, inp.context_lens, inp.block_tables,
+                               inp.softmax_scale, c.query_len, inp.max_context, torch.bfloat16, None,
+                               inp.key_scale, inp.value_scale, None, c.partition_size, None, None, None, status, None)
+    else:
+        p = decoder.params
     L = _lib.lib()
     stream = torch.cuda.current_stream().cuda_stream
     n_k = max(20, min(args.steps, 200))
@@ -267,10 +303,10 @@ def run_ours(args, rank: int, world: int, local: int):
 
     # ---- end to end: the step's inputs arrive from pinned host memory, the output goes back
     hq = inp.query.cpu().pin_memory()
-    hctx = inp.context_lens.cpu().pin_memory()
-    hbt = inp.block_tables.cpu().pin_memory()
+    hctx = step_ctx.cpu().pin_memory()
+    hbt = step_bt.cpu().pin_memory()
     hout = torch.empty_like(out, device="cpu").pin_memory()
-    dq, dctx, dbt = torch.empty_like(inp.query), torch.empty_like(inp.context_lens), torch.empty_like(inp.block_tables)
+    dq, dctx, dbt = torch.empty_like(inp.query), torch.empty_like(step_ctx), torch.empty_like(step_bt)
 
     def e2e_step():
         dq.copy_(hq, non_blocking=True)
@@ -319,7 +355,7 @@ def run_ours(args, rank: int, world: int, local: int):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "us_per_call": ms_step * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "higher_is_better": True, "scaling": "weak" if mode == "sequences-weak" else "strong", "vs_baseline": None,
         "dtype": "bf16 x bf16 -> f32" if c.kv_dtype == "bf16" else "e4m3 x e4m3 -> f32",
         "data": "synthetic",
         "pct_of_nominal_hbm": 100.0 * value / (NOMINAL_HBM_GBS * world),
@@ -329,7 +365,10 @@ def run_ours(args, rank: int, world: int, local: int):
                    "kv": ("bf16" if c.kv_dtype == "bf16" else "fp8 e4m3fn") + ", " + c.quant.replace("_", "-") + " scales",
                    "partition_size": c.partition_size, "kv_bytes_per_gpu": kv_bytes,
                    "l2": "inputs larger than L2 (KV read per step: %.0f MB per GPU)" % (kv_bytes / 1e6),
-                   "sharding": "sequences, no collective"},
+                   "sharding": {"sequences-weak": "sequences, one full batch per GPU, no collective",
+                                "sequences-strong": "one batch, sequences dealt out by token count, no collective",
+                                "kv-partitions": "KV partition ranges per GPU; (max, sum, out) triples "
+                                                 "all-gathered over NCCL and merged"}[mode]},
         "roofline": {"bound": "hbm", "kernel": "partition kernel (pa_partition_sm100)", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind + " (torch copy_, read+write)", "unit": "GB/s", "frac": achieved / peak,
                      "us_per_launch": us_partition, "algorithmic_bytes": kv_bytes,
@@ -339,7 +378,7 @@ def run_ours(args, rank: int, world: int, local: int):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "note": "query, block tables and context lengths from pinned host memory, output copied back; "
                         "the KV cache is resident state, as in serving"},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": (2 if decoder is None else decoder.launches_per_step) * args.steps,
         "clocks": clocks,
         "device_status": dev_status,
     }
@@ -354,6 +393,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2_llama8b", choices=sorted(CONFIGS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sharding", default="auto",
+                    choices=["auto", "sequences-weak", "sequences-strong", "kv-partitions"],
+                    help="multi-GPU split; auto = KV partitions for the long-context workload, else one batch per GPU")
     ap.add_argument("--num-seqs", type=int, default=0,
                     help="override the workload's batch size (profiler captures of the large workloads)")
     args = ap.parse_args()

@@ -15,13 +15,18 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr unsigned kFullMask = 0xffffffffu;
 
-// Upper bound on polls of one mbarrier phase.  The first kSpinPolls polls go back to back (a
-// sleeping waiter would add its wake-up latency to every hand-off of the pipeline); after that
-// the waiter sleeps between polls, so the limit is of the order of a second while a healthy
-// copy completes in microseconds.  When the limit runs out the warp records
-// PA_DEV_WAIT_TIMEOUT and stops issuing work, so a lost copy can never spin a GPU forever.
+// Upper bound on polls of one mbarrier phase.  A poll is a try_wait with a suspend-time hint:
+// the hardware parks the thread until the phase completes or the hint runs out, so a waiting
+// warp takes few issue slots from the warps that compute (back-to-back polls of the four
+// waiting roles were more than half of all instructions the kernel issued), and wakes as soon
+// as the phase completes.  After kSpinPolls polls the waiter also sleeps between polls.  The
+// limit is of the order of seconds if every poll runs its full hint and tens of milliseconds
+// if the hint is ignored, while a healthy copy completes in microseconds.  When the limit runs
+// out the warp records PA_DEV_WAIT_TIMEOUT and stops issuing work, so a lost copy can never
+// spin a GPU forever.
 constexpr uint32_t kSpinPolls = 1u << 15;
-constexpr uint32_t kWaitPollLimit = 1u << 22;
+constexpr uint32_t kWaitPollLimit = 1u << 20;
+constexpr uint32_t kPollSuspendNs = 4096;
 
 // Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may
 // start while its predecessor still runs; it must call grid_dependency_wait() before touching
@@ -69,13 +74,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return done != 0;
+}
+
 // Bounded wait; false when the limit ran out.  The polling loop is one shared out-of-line
 // function: inlined at every wait site (and unrolled) it made up almost half of the kernel's
 // code, and the kernels' hot loops should stay inside the instruction cache.
 __device__ __noinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity) {
 #pragma unroll 1
   for (uint32_t it = 0; it < kWaitPollLimit; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, kPollSuspendNs)) return true;
     if (it > kSpinPolls) __nanosleep(200);
   }
   return false;
