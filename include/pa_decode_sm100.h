@@ -164,6 +164,17 @@ int pa_merge_triples_sm100(void* out, int64_t out_stride_row, const float* m, co
                            const float* o, int32_t num_shards, int32_t num_rows, int32_t head_size,
                            void* stream);
 
+/*
+ * The same merge on triples packed for a single all-gather (no counterpart in the reference).
+ * One shard's message is pa_packed_triple_floats(num_rows, head_size) floats:
+ *   m[num_rows] | l[num_rows] | padding to a multiple of 4 floats | o[num_rows][head_size]
+ * (point pa_reduce_sm100's tri_m / tri_l / tri_o into such a buffer); `packed` holds
+ * num_shards messages back to back, as an all-gather leaves them.
+ */
+int64_t pa_packed_triple_floats(int32_t num_rows, int32_t head_size);
+int pa_merge_packed_triples_sm100(void* out, int64_t out_stride_row, const float* packed,
+                                  int32_t num_shards, int32_t num_rows, int32_t head_size, void* stream);
+
 /* Bytes of dynamic shared memory and the grid the partition kernel would use for `params`
  * (host-only query, launches nothing).  Any output pointer may be NULL. */
 int pa_query_launch_sm100(const PaDecodeParams* params, int32_t* grid_ctas, int32_t* cta_threads,

@@ -81,3 +81,25 @@ def test_prepared_decoder_single_rank_equals_operator():
     single, _ = run_operator(inp)
     single = pack_mtp(single, cfg.num_seqs, cfg.query_len, cfg.kv_heads)
     assert (got.float() - single.float()).abs().max().item() < 8e-3     # fp32 triple, then one bf16 rounding
+
+
+def test_packed_merge_equals_plain_merge():
+    import ctypes as C
+    from triton_op_b200 import _lib
+    L = _lib.lib()
+    W, R, D = 3, 21, 128                      # 2R = 42 floats: the o block starts after 2 floats of padding
+    n = int(L.pa_packed_triple_floats(R, D))
+    assert n == 44 + R * D
+    g = torch.Generator(device="cuda:0")
+    g.manual_seed(9)
+    m = torch.randn(W, R, device="cuda:0", generator=g)
+    l = torch.rand(W, R, device="cuda:0", generator=g) + 0.1
+    o = torch.randn(W, R, D, device="cuda:0", generator=g)
+    packed = torch.full((W, n), float("nan"), device="cuda:0")
+    packed[:, :R], packed[:, R:2 * R], packed[:, 44:] = m, l, o.reshape(W, -1)
+    out = torch.empty(R, D, dtype=torch.bfloat16, device="cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    _lib.check(L.pa_merge_packed_triples_sm100(out.data_ptr(), D, packed.data_ptr(), W, R, D, stream), "packed merge")
+    want = merge_triples_cuda(m, l, o)
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)

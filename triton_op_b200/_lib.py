@@ -22,7 +22,7 @@ PA_NOALLOC_SCRATCH_BYTES = 16 << 20
 
 EXPORTS = (
     "pa_decode_sm100", "pa_decode_noalloc_sm100", "pa_partition_sm100", "pa_reduce_sm100", "pa_merge_triples_sm100",
-    "pa_query_launch_sm100", "pa_strerror", "pa_last_cuda_error", "pa_abi_version",
+    "pa_merge_packed_triples_sm100", "pa_packed_triple_floats", "pa_query_launch_sm100", "pa_strerror", "pa_last_cuda_error", "pa_abi_version",
 )
 
 
@@ -81,6 +81,11 @@ def lib() -> C.CDLL:
     L.pa_reduce_sm100.argtypes = [P, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.pa_merge_triples_sm100.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                          C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
+    L.pa_merge_packed_triples_sm100.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                                C.c_void_p]
+    L.pa_merge_packed_triples_sm100.restype = C.c_int
+    L.pa_packed_triple_floats.argtypes = [C.c_int32, C.c_int32]
+    L.pa_packed_triple_floats.restype = C.c_int64
     L.pa_query_launch_sm100.argtypes = [P] + [C.POINTER(C.c_int32)] * 4
     for name in ("pa_decode_sm100", "pa_decode_noalloc_sm100", "pa_partition_sm100", "pa_reduce_sm100",
                  "pa_merge_triples_sm100", "pa_query_launch_sm100", "pa_last_cuda_error",

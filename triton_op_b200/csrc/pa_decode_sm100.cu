@@ -520,21 +520,46 @@ int pa_decode_noalloc_sm100(const PaDecodeParams* params, void* stream) {
   return pa_decode_sm100(&q, stream);
 }
 
-int pa_merge_triples_sm100(void* out, int64_t out_stride_row, const float* m, const float* l,
-                           const float* o, int32_t num_shards, int32_t num_rows, int32_t head_size,
-                           void* stream) {
+namespace {
+int launch_merge(void* out, int64_t out_stride_row, const float* m, const float* l, const float* o,
+                 int32_t num_shards, int32_t num_rows, int32_t head_size, int64_t ml_stride,
+                 int64_t o_stride, void* stream) {
   if (!out || !m || !l || !o) return PA_ERR_NULL_POINTER;
   if (num_shards <= 0 || num_rows < 0) return PA_ERR_BAD_SHAPE;
   if (head_size != pa::kD) return PA_ERR_UNSUPPORTED;
-  if (!aligned16(o) || (reinterpret_cast<uintptr_t>(out) & 7u) || (out_stride_row & 3))
+  if (!aligned16(o) || (o_stride & 3) || (reinterpret_cast<uintptr_t>(out) & 7u) || (out_stride_row & 3))
     return PA_ERR_ALIGNMENT;
   if (num_rows == 0) return PA_OK;
   const int blocks = (num_rows + 3) / 4;
   pa::pa_merge_triples_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<uint8_t*>(out), out_stride_row, m, l, o, num_shards, num_rows);
+      static_cast<uint8_t*>(out), out_stride_row, m, l, o, num_shards, num_rows, ml_stride, o_stride);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return PA_OK;
+}
+}  // namespace
+
+int pa_merge_triples_sm100(void* out, int64_t out_stride_row, const float* m, const float* l,
+                           const float* o, int32_t num_shards, int32_t num_rows, int32_t head_size,
+                           void* stream) {
+  return launch_merge(out, out_stride_row, m, l, o, num_shards, num_rows, head_size, num_rows,
+                      (int64_t)num_rows * head_size, stream);
+}
+
+int64_t pa_packed_triple_floats(int32_t num_rows, int32_t head_size) {
+  if (num_rows < 0 || head_size <= 0) return 0;
+  const int64_t ml = ((int64_t)2 * num_rows + 3) & ~(int64_t)3;
+  return ml + (int64_t)num_rows * head_size;
+}
+
+int pa_merge_packed_triples_sm100(void* out, int64_t out_stride_row, const float* packed,
+                                  int32_t num_shards, int32_t num_rows, int32_t head_size, void* stream) {
+  if (!packed) return PA_ERR_NULL_POINTER;
+  if (num_rows < 0 || head_size <= 0) return PA_ERR_BAD_SHAPE;
+  const int64_t stride = pa_packed_triple_floats(num_rows, head_size);
+  const int64_t o_off = stride - (int64_t)num_rows * head_size;
+  return launch_merge(out, out_stride_row, packed, packed + num_rows, packed + o_off, num_shards, num_rows,
+                      head_size, stride, stride, stream);
 }
 
 int pa_query_launch_sm100(const PaDecodeParams* params, int32_t* grid_ctas, int32_t* cta_threads,

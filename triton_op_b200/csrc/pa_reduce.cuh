@@ -125,28 +125,29 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(const __grid_constant__ 
   }
 }
 
-// One warp per row; merges `num_shards` (m, l, o) triples.
+// One warp per row; merges `num_shards` (m, l, o) triples.  Shard s keeps its m and l rows
+// ml_stride floats and its o rows o_stride floats after those of shard s - 1.
 __global__ void __launch_bounds__(128)
 pa_merge_triples_kernel(uint8_t* out, int64_t out_stride_row, const float* __restrict__ m,
                         const float* __restrict__ l, const float* __restrict__ o, int num_shards,
-                        int num_rows) {
+                        int num_rows, int64_t ml_stride, int64_t o_stride) {
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= num_rows) return;
   float M = -INFINITY;
   for (int s = 0; s < num_shards; ++s) {
-    const float ls = l[(int64_t)s * num_rows + row];
-    const float ms = m[(int64_t)s * num_rows + row];
+    const float ls = l[(int64_t)s * ml_stride + row];
+    const float ms = m[(int64_t)s * ml_stride + row];
     if (ls > 0.f) M = fmaxf(M, ms);
   }
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   float W = 0.f;
   for (int s = 0; s < num_shards; ++s) {
-    const float ls = l[(int64_t)s * num_rows + row];
-    const float ms = m[(int64_t)s * num_rows + row];
+    const float ls = l[(int64_t)s * ml_stride + row];
+    const float ms = m[(int64_t)s * ml_stride + row];
     if (!(ls > 0.f) || !(ms > -INFINITY)) continue;
     const float w = ls * expf(ms - M);
-    const float4 v = *reinterpret_cast<const float4*>(o + ((int64_t)s * num_rows + row) * kD + 4 * lane);
+    const float4 v = *reinterpret_cast<const float4*>(o + (int64_t)s * o_stride + row * kD + 4 * lane);
     W += w;
     acc[0] = fmaf(w, v.x, acc[0]);
     acc[1] = fmaf(w, v.y, acc[1]);

@@ -265,7 +265,7 @@ class KvShardedDecoder:
 
     The parameter block, the local block tables, the workspaces and the exchange buffers are
     built in the constructor; :meth:`step` then only launches (partition kernel, reduce kernel
-    with triples, two all-gathers, merge kernel), so a decode loop pays no per-step host work
+    with triples, one all-gather, merge kernel), so a decode loop pays no per-step host work
     beyond the launches.  The kernels read the context lengths from device memory on every
     step, so ``self.context_lens`` may be updated in place between steps as sequences grow
     within their last partition.  Restricted to batches whose ranges need one launch
@@ -297,19 +297,19 @@ class KvShardedDecoder:
         self.context_lens = torch.tensor(lens, dtype=torch.int32).to(dev)
         self.kv_bytes = sum(lens) * key_cache.shape[1] * D * 2 * key_cache.element_size()
         self._scratch_out = torch.empty_like(query)
-        self.ml = torch.empty((2, R), dtype=torch.float32, device=dev)      # m row, l row: one message
-        self.o = torch.empty((R, D), dtype=torch.float32, device=dev)
-        self.ml_all = torch.empty((self.world * 2, R), dtype=torch.float32, device=dev)
-        self.o_all = torch.empty((self.world * R, D), dtype=torch.float32, device=dev)
-        self.m_all = torch.empty((self.world, R), dtype=torch.float32, device=dev)
-        self.l_all = torch.empty((self.world, R), dtype=torch.float32, device=dev)
+        self._lib = _lib
+        self._L = _lib.lib()
+        # this rank's message m | l | pad | o, and the gathered messages of all ranks
+        self.msg_floats = int(self._L.pa_packed_triple_floats(R, D))
+        self.msg = torch.empty(self.msg_floats, dtype=torch.float32, device=dev)
+        self.msg_all = torch.empty(self.world * self.msg_floats, dtype=torch.float32, device=dev)
+        self._o_off = self.msg_floats - R * D
+        self._rows = R
         self.out = torch.empty((S, rows, D), dtype=torch.bfloat16, device=dev)
         self.params, self._keep = build_params(
             self._scratch_out, query, key_cache, value_cache, self.context_lens, self.tables, softmax_scale,
             kinds[0] if kinds else 1, max(lens + [1]), None, None, key_scale, value_scale, None, partition_size,
             None, None, None, status, None)
-        self._lib = _lib
-        self._L = _lib.lib()
         self.launches_per_step = 3
 
     def step(self) -> torch.Tensor:
@@ -317,22 +317,17 @@ class KvShardedDecoder:
         ``[S, Hkv*L*G, D]`` (the same tensor every step)."""
         import torch.distributed as dist
         L, lib = self._L, self._lib
-        R, D = self.o.shape
+        R, D = self._rows, self.out.shape[-1]
+        base = self.msg.data_ptr()
         with torch.cuda.device(self.query.device):
             stream = torch.cuda.current_stream().cuda_stream
             lib.check(L.pa_partition_sm100(C.byref(self.params), stream), "pa_partition_sm100")
-            lib.check(L.pa_reduce_sm100(C.byref(self.params), self.ml[0].data_ptr(), self.ml[1].data_ptr(),
-                                        self.o.data_ptr(), stream), "pa_reduce_sm100")
-            if self.world > 1:
-                dist.all_gather_into_tensor(self.ml_all, self.ml, group=self.group)
-                dist.all_gather_into_tensor(self.o_all, self.o, group=self.group)
-                src = self.ml_all.view(self.world, 2, R)
-                self.m_all.copy_(src[:, 0])
-                self.l_all.copy_(src[:, 1])
-                m_all, l_all, o_all = self.m_all, self.l_all, self.o_all
-            else:
-                m_all, l_all, o_all = self.ml[0:1], self.ml[1:2], self.o
-            flat = self.out.view(R, D)
-            lib.check(L.pa_merge_triples_sm100(flat.data_ptr(), D, m_all.data_ptr(), l_all.data_ptr(),
-                                               o_all.data_ptr(), self.world, R, D, stream), "pa_merge_triples_sm100")
+            lib.check(L.pa_reduce_sm100(C.byref(self.params), base, base + 4 * R, base + 4 * self._o_off, stream),
+                      "pa_reduce_sm100")
+            gathered = self.msg
+            if self.world > 1:      # one collective per step
+                dist.all_gather_into_tensor(self.msg_all, self.msg, group=self.group)
+                gathered = self.msg_all
+            lib.check(L.pa_merge_packed_triples_sm100(self.out.data_ptr(), D, gathered.data_ptr(), self.world, R, D,
+                                                      stream), "pa_merge_packed_triples_sm100")
         return self.out
