@@ -217,3 +217,18 @@ def test_baseline_configs_reduced_batch(name, num_seqs):
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     assert_close(out, ref, what=name)
+
+
+@pytest.mark.parametrize("lens,psize,ql", [([12000, 100, 4096], 256, 1),       # 47 partitions: 4 warps per row
+                                            ([40000, 9000, 300], 256, 2),      # 157 partitions: 16 warps per row
+                                            ([70000, 513], 512, 1)])           # 137 partitions of 512 tokens
+def test_long_contexts_use_the_multi_warp_reduce(lens, psize, ql):
+    """Rows with more than 32 partitions are merged by several warps; the result must not depend on
+    how the partitions were dealt out, so it is compared with the oracle and with the triples path."""
+    from triton_op_b200.inputs import DecodeConfig, make_inputs
+    cfg = DecodeConfig("long", len(lens), 4 * ql, 1, 16, ql, ("fixed", 1), partition_size=psize)
+    inp = make_inputs(cfg, seed=21, device=DEV, context_lens=torch.tensor(lens))
+    out, res = run_operator(inp)
+    torch.cuda.synchronize()
+    assert res["exponential_sums"].shape[2] > 32
+    assert_close(out, oracle_output(inp), what=f"{lens} partition {psize}")

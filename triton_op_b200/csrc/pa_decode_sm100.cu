@@ -411,13 +411,15 @@ int launch_reduce(const PaDecodeParams* p, float* tri_m, float* tri_l, float* tr
   r.tmp_stride_row = p->tmp_stride_row;
   const int64_t rows = (int64_t)r.S * r.Hkv * r.eqG;
   if (rows == 0) return PA_OK;
-  const int64_t blocks = (rows + 3) / 4;
+  // warps per row: one while a row has at most one chunk of 32 partitions, more for long contexts
+  const int wpr = r.max_partitions <= 32 ? 1 : (r.max_partitions <= 128 ? 4 : 16);
+  const int64_t blocks = wpr == 1 ? (rows + 3) / 4 : rows;
   if (blocks > 0x7fffffff) return PA_ERR_TOO_LARGE;
   // Programmatic dependent launch: the reduce grid may be scheduled while the partition kernel
   // drains; it waits (griddepcontrol.wait) before it reads anything that kernel wrote.
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks);
-  cfg.blockDim = dim3(128);
+  cfg.blockDim = dim3(wpr == 16 ? 512 : 128);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -425,7 +427,9 @@ int launch_reduce(const PaDecodeParams* p, float* tri_m, float* tri_l, float* tr
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, pa::pa_reduce_kernel, r);
+  cudaError_t e = wpr == 1   ? cudaLaunchKernelEx(&cfg, pa::pa_reduce_kernel<1>, r)
+                  : wpr == 4 ? cudaLaunchKernelEx(&cfg, pa::pa_reduce_kernel<4>, r)
+                             : cudaLaunchKernelEx(&cfg, pa::pa_reduce_kernel<16>, r);
   if (e != cudaSuccess) return cuda_fail(e);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);

@@ -29,12 +29,21 @@ struct ReduceParams {
   int64_t tmp_stride_seq, tmp_stride_head, tmp_stride_part, tmp_stride_row;
 };
 
-// One warp per output row (sequence, kv head, row r); lane owns head dims 4*lane..4*lane+3.
-__global__ void __launch_bounds__(128) pa_reduce_kernel(const __grid_constant__ ReduceParams p) {
+// WPR warps per output row (sequence, kv head, row r); lane owns head dims 4*lane..4*lane+3.
+// WPR = 1: four rows per CTA, the usual case (np <= 32: one chunk).  Long contexts have few rows
+// and hundreds of partitions each, and a single warp would walk them one memory round trip
+// after the other; with WPR = 4 or 16 the warps of a CTA take the 32-partition chunks of ONE row
+// round-robin and combine their running (max, sum, weighted output) through shared memory.
+template <int WPR>
+__global__ void __launch_bounds__(WPR == 16 ? 512 : 128) pa_reduce_kernel(const __grid_constant__ ReduceParams p) {
+  constexpr int kWarps = WPR == 16 ? 16 : 4;
+  constexpr int kRowsPerCta = kWarps / WPR;
   const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int warp = threadIdx.x >> 5;
+  const int slice = warp % WPR;
+  const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + warp / WPR;
   const int64_t n_rows = (int64_t)p.S * p.Hkv * p.eqG;
-  if (row >= n_rows) return;
+  if (row >= n_rows) return;   // WPR > 1: one row per CTA, so the whole CTA leaves together
   const int r = (int)(row % p.eqG);
   const int head = (int)((row / p.eqG) % p.Hkv);
   const int seq = (int)(row / ((int64_t)p.eqG * p.Hkv));
@@ -53,12 +62,12 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(const __grid_constant__ 
   grid_dependency_wait();
 
   // Partitions are taken 32 at a time (lane = partition for the max / weight, then eight
-  // partial-output rows in flight per step) with a running maximum, so the whole row costs
-  // about one global-memory round trip for the usual np <= 32.
+  // partial-output rows in flight per step) with a running maximum, so a chunk costs about
+  // one global-memory round trip.
   float M = -INFINITY;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   float W = 0.f;
-  for (int p0 = 0; p0 < np; p0 += 32) {
+  for (int p0 = slice * 32; p0 < np; p0 += 32 * WPR) {
     const int pi = p0 + lane;
     const int cnt = min(32, np - p0);
     float m = -INFINITY, l = 0.f;
@@ -103,6 +112,37 @@ __global__ void __launch_bounds__(128) pa_reduce_kernel(const __grid_constant__ 
         }
       }
     }
+  }
+  if (WPR > 1) {
+    // combine the warps' partial results: warp `slice` holds (M, W, acc) of its chunks
+    __shared__ float s_m[kWarps], s_w[kWarps];
+    __shared__ float4 s_acc[kWarps][32];
+    if (lane == 0) {
+      s_m[slice] = M;
+      s_w[slice] = W;
+    }
+    s_acc[slice][lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncthreads();
+    if (slice != 0) return;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < WPR; ++s) mx = fmaxf(mx, s_m[s]);
+    W = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int s = 0; s < WPR; ++s) {
+      const float ms = s_m[s];
+      if (!(ms > -INFINITY)) continue;    // that warp saw no partition with weight
+      const float f = expf(ms - mx);
+      const float4 a = s_acc[s][lane];
+      W = fmaf(s_w[s], f, W);
+      acc[0] = fmaf(a.x, f, acc[0]);
+      acc[1] = fmaf(a.y, f, acc[1]);
+      acc[2] = fmaf(a.z, f, acc[2]);
+      acc[3] = fmaf(a.w, f, acc[3]);
+    }
+    M = mx;
   }
   const float inv = W > 0.f ? 1.0f / W : 0.f;
 #pragma unroll

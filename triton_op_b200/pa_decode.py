@@ -32,9 +32,20 @@ class PaArgumentError(AssertionError, ValueError):
     1742-1790); deriving from both lets either style of caller catch it."""
 
 
-def _require(cond: bool, msg: str) -> None:
-    if not cond:
-        raise PaArgumentError(msg)
+def _fail(msg: str) -> None:
+    raise PaArgumentError(msg)
+
+
+def _inner_contiguous(t: torch.Tensor, first_dim: int) -> bool:
+    """True when dims ``first_dim..`` of ``t`` are laid out densely (what ``t[0, 0].is_contiguous()``
+    says for ``first_dim = 2``, without creating views)."""
+    expect = 1
+    shape, stride = t.shape, t.stride()
+    for d in range(t.dim() - 1, first_dim - 1, -1):
+        if shape[d] != 1 and stride[d] != expect:
+            return False
+        expect *= shape[d]
+    return True
 
 
 def _next_pow2(n: int) -> int:
@@ -103,13 +114,40 @@ def _kv_scale(scale, other, name: str, device) -> Tuple[Optional[torch.Tensor], 
         return None, _lib.PA_QUANT_NONE
     if isinstance(scale, (int, float)):
         return _scalar_on_device(float(scale), device), _lib.PA_QUANT_PER_TENSOR
-    _require(isinstance(scale, torch.Tensor) and scale.dtype == torch.float32,
-             f"{name} tensor only support dtype == torch.float32, but got {name}.dtype == {getattr(scale, 'dtype', type(scale))}")
+    if not (isinstance(scale, torch.Tensor) and scale.dtype == torch.float32):
+        _fail(f"{name} tensor only support dtype == torch.float32, but got {name}.dtype == {getattr(scale, 'dtype', type(scale))}")
     if scale.dim() == 0 or scale.numel() == 1:
         return scale.reshape(()), _lib.PA_QUANT_PER_TENSOR
-    _require(scale.dim() == 4, f"Expected 4D {name} tensor, but got shape {tuple(scale.shape)}")
-    _require(scale.shape[-1] == 1, f"Expected {name}.shape[-1] == 1, but got {name}.shape[-1]={scale.shape[-1]}")
+    if not (scale.dim() == 4):
+        _fail(f"Expected 4D {name} tensor, but got shape {tuple(scale.shape)}")
+    if not (scale.shape[-1] == 1):
+        _fail(f"Expected {name}.shape[-1] == 1, but got {name}.shape[-1]={scale.shape[-1]}")
     return scale, _lib.PA_QUANT_PER_TOKEN
+
+
+_PARAM_CACHE: Dict[tuple, PaDecodeParams] = {}
+
+
+def _tensor_key(t) -> tuple:
+    if t is None or not isinstance(t, torch.Tensor):
+        return (t,)
+    return (t.data_ptr(), t.shape, t.stride(), t.dtype)
+
+
+def _params_key(output, query, key_cache, value_cache, sequence_lengths, block_tables, softmax_scale,
+                query_sequence_length, max_sequence_length, compute_type, query_scale, key_scale, value_scale,
+                alibi_slopes, partition_size, exp_sums, max_logits, tmp_output, status) -> Optional[tuple]:
+    """Everything the parameter block depends on: addresses, shapes, strides, dtypes, scalars.
+    A decode loop calls with the same tensors every step, and validating them and filling the
+    60-field block costs more host time than a small batch takes on the GPU."""
+    try:
+        return (str(output.device), float(softmax_scale), int(query_sequence_length), int(max_sequence_length),
+                str(compute_type), int(partition_size)) + tuple(
+            _tensor_key(t) for t in (output, query, key_cache, value_cache, sequence_lengths, block_tables,
+                                     query_scale, key_scale, value_scale, alibi_slopes, exp_sums, max_logits,
+                                     tmp_output, status))
+    except Exception:     # unexpected argument types: take the validating path, which reports them
+        return None
 
 
 def build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
@@ -117,67 +155,107 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
                  compute_type, query_scale, key_scale, value_scale, alibi_slopes,
                  partition_size: int, exp_sums, max_logits, tmp_output, status, tune
                  ) -> Tuple[PaDecodeParams, tuple]:
+    """Validated C parameter block for the arguments, from a small cache when the same tensors
+    (addresses, shapes, strides, dtypes) and scalars were validated before."""
+    key = None
+    if tune is None:
+        key = _params_key(output, query, key_cache, value_cache, sequence_lengths, block_tables, softmax_scale,
+                          query_sequence_length, max_sequence_length, compute_type, query_scale, key_scale,
+                          value_scale, alibi_slopes, partition_size, exp_sums, max_logits, tmp_output, status)
+        hit = _PARAM_CACHE.get(key) if key is not None else None
+        if hit is not None:
+            p, ws = hit
+            return p, (output, query, key_cache, value_cache, sequence_lengths, block_tables, query_scale,
+                       key_scale, value_scale, alibi_slopes) + ws + (status,)
+    p, keep, cacheable = _build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
+                                       softmax_scale, query_sequence_length, max_sequence_length, compute_type,
+                                       query_scale, key_scale, value_scale, alibi_slopes, partition_size,
+                                       exp_sums, max_logits, tmp_output, status, tune)
+    if key is not None and cacheable:
+        if len(_PARAM_CACHE) >= 16:
+            _PARAM_CACHE.clear()
+        _PARAM_CACHE[key] = (p, keep[10:13])    # the block and the workspaces it points into
+    return p, keep
+
+
+def _build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
+                 softmax_scale: float, query_sequence_length: int, max_sequence_length: int,
+                 compute_type, query_scale, key_scale, value_scale, alibi_slopes,
+                 partition_size: int, exp_sums, max_logits, tmp_output, status, tune
+                 ) -> Tuple[PaDecodeParams, tuple, bool]:
     """Validates the arguments as the reference does and fills the C parameter block.
 
-    Returns the block and a tuple of the tensors it points into (keep it alive across the call).
+    Returns the block, a tuple of the tensors it points into (keep it alive across the call) and
+    whether the block points only at the caller's tensors and the cached workspaces (then it
+    may be reused for the same arguments).
     """
-    _require(isinstance(output, torch.Tensor), "output must be a torch.Tensor")
+    given = (query, sequence_lengths, block_tables, query_scale, key_scale, value_scale)
+    if not (isinstance(output, torch.Tensor)):
+        _fail("output must be a torch.Tensor")
     dev = output.device
-    _require(len(output.shape) == 3, f"Expected 3D output tensor, but got shape {tuple(output.shape)}")
-    _require(len(query.shape) == 3, f"Expected 3D query tensor, but got shape {tuple(query.shape)}")
-    _require(len(key_cache.shape) == 5, f"Expected 5D key_cache tensor, but got shape {tuple(key_cache.shape)}")
+    if not (len(output.shape) == 3):
+        _fail(f"Expected 3D output tensor, but got shape {tuple(output.shape)}")
+    if not (len(query.shape) == 3):
+        _fail(f"Expected 3D query tensor, but got shape {tuple(query.shape)}")
+    if not (len(key_cache.shape) == 5):
+        _fail(f"Expected 5D key_cache tensor, but got shape {tuple(key_cache.shape)}")
     if len(value_cache.shape) == 5:
         v_layout = _lib.PA_V_TRANSPOSED
     elif len(value_cache.shape) == 4:
         v_layout = _lib.PA_V_NORMAL
     else:
         raise RuntimeError(f"Unsupported value cache shape: {tuple(value_cache.shape)}")
-    _require(output.dtype == torch.bfloat16,
-             f"output tensor only support dtype == torch.bfloat16, but got output.dtype == {output.dtype}")
-    _require(_compute_type_matches(compute_type, output.dtype),
-             f"compute_type {compute_type} disagrees with output.dtype {output.dtype}")
+    if not (output.dtype == torch.bfloat16):
+        _fail(f"output tensor only support dtype == torch.bfloat16, but got output.dtype == {output.dtype}")
+    if not (_compute_type_matches(compute_type, output.dtype)):
+        _fail(f"compute_type {compute_type} disagrees with output.dtype {output.dtype}")
     q_dtype = _dtype_code(query.dtype, "query")
     kv_dtype = _dtype_code(key_cache.dtype, "key_cache")
-    _require(value_cache.dtype == key_cache.dtype,
-             f"value_cache.dtype {value_cache.dtype} != key_cache.dtype {key_cache.dtype}")
+    if not (value_cache.dtype == key_cache.dtype):
+        _fail(f"value_cache.dtype {value_cache.dtype} != key_cache.dtype {key_cache.dtype}")
     for name, t in (("query", query), ("key_cache", key_cache), ("value_cache", value_cache),
                     ("sequence_lengths", sequence_lengths), ("block_tables", block_tables)):
-        _require(t.device == dev, f"{name} must live on {dev}, the output's device")
-    _require(sequence_lengths.dtype == torch.int32 and block_tables.dtype == torch.int32,
-             "sequence_lengths and block_tables must be int32")
-    _require(query_sequence_length >= 1, "query_sequence_length must be >= 1")
-    _require(query_sequence_length <= 4,
-             f"QUERY_SEQ_LEN={query_sequence_length}, Only support QUERY_SEQ_LEN <= 4")
+        if not (t.device == dev):
+            _fail(f"{name} must live on {dev}, the output's device")
+    if not (sequence_lengths.dtype == torch.int32 and block_tables.dtype == torch.int32):
+        _fail("sequence_lengths and block_tables must be int32")
+    if not (query_sequence_length >= 1):
+        _fail("query_sequence_length must be >= 1")
+    if not (query_sequence_length <= 4):
+        _fail(f"QUERY_SEQ_LEN={query_sequence_length}, Only support QUERY_SEQ_LEN <= 4")
 
     num_seqs, q_heads_total, head_size = query.shape
-    _require(tuple(output.shape) == tuple(query.shape), "output and query must have the same shape")
+    if not (tuple(output.shape) == tuple(query.shape)):
+        _fail("output and query must have the same shape")
     num_blocks, num_kv_heads = key_cache.shape[0], key_cache.shape[1]
     kv_block_size = key_cache.shape[-2]
     x = 16 // key_cache.element_size()
-    _require(key_cache.shape[2] * key_cache.shape[4] == head_size and key_cache.shape[4] == x,
-             f"key_cache must be [num_blocks, num_kv_heads, head_size/{x}, block_size, {x}]")
-    _require(kv_block_size in SUPPORTED_BLOCK_SIZES,
-             f"kv_block_size == {kv_block_size} not in {list(SUPPORTED_BLOCK_SIZES)}")
+    if not (key_cache.shape[2] * key_cache.shape[4] == head_size and key_cache.shape[4] == x):
+        _fail(f"key_cache must be [num_blocks, num_kv_heads, head_size/{x}, block_size, {x}]")
+    if not (kv_block_size in SUPPORTED_BLOCK_SIZES):
+        _fail(f"kv_block_size == {kv_block_size} not in {list(SUPPORTED_BLOCK_SIZES)}")
     heads_per_token = q_heads_total // query_sequence_length
-    _require(heads_per_token * query_sequence_length == q_heads_total and heads_per_token % num_kv_heads == 0,
-             "query heads must be num_kv_heads * query_sequence_length * group_size")
+    if not (heads_per_token * query_sequence_length == q_heads_total and heads_per_token % num_kv_heads == 0):
+        _fail("query heads must be num_kv_heads * query_sequence_length * group_size")
     group = heads_per_token // num_kv_heads
     eq_group = group * query_sequence_length
     eq_group_pow2 = 16 if eq_group <= 16 else _next_pow2(eq_group)
-    _require(eq_group_pow2 <= 64, f"equivalent_query_group_size_pow2={eq_group_pow2} exceeds maximum of 64")
+    if not (eq_group_pow2 <= 64):
+        _fail(f"equivalent_query_group_size_pow2={eq_group_pow2} exceeds maximum of 64")
     if v_layout == _lib.PA_V_NORMAL:
-        _require(tuple(value_cache.shape) == (num_blocks, num_kv_heads, head_size, kv_block_size),
-                 "value_cache must be [num_blocks, num_kv_heads, head_size, block_size]")
-    _require(block_tables.dim() == 2 and block_tables.shape[0] == num_seqs and sequence_lengths.numel() == num_seqs,
-             "block_tables must be [num_seqs, max_blocks] and sequence_lengths [num_seqs]")
-    _require(partition_size > 0 and (partition_size % kv_block_size == 0 or kv_block_size % partition_size == 0),
-             "partition_size and block_size must divide one another")
+        if not (tuple(value_cache.shape) == (num_blocks, num_kv_heads, head_size, kv_block_size)):
+            _fail("value_cache must be [num_blocks, num_kv_heads, head_size, block_size]")
+    if not (block_tables.dim() == 2 and block_tables.shape[0] == num_seqs and sequence_lengths.numel() == num_seqs):
+        _fail("block_tables must be [num_seqs, max_blocks] and sequence_lengths [num_seqs]")
+    if not (partition_size > 0 and (partition_size % kv_block_size == 0 or kv_block_size % partition_size == 0)):
+        _fail("partition_size and block_size must divide one another")
 
     if query.stride(-1) != 1 or query.stride(1) != head_size:
         query = query.contiguous()
-    _require(output.stride(-1) == 1, "output's last dim must be contiguous")
-    _require(key_cache[0, 0].is_contiguous() and value_cache[0, 0].is_contiguous(),
-             "the per-(block, head) slabs of the KV caches must be contiguous")
+    if not (output.stride(-1) == 1):
+        _fail("output's last dim must be contiguous")
+    if not (_inner_contiguous(key_cache, 2) and _inner_contiguous(value_cache, 2)):
+        _fail("the per-(block, head) slabs of the KV caches must be contiguous")
     if sequence_lengths.stride(0) != 1:
         sequence_lengths = sequence_lengths.contiguous()
     if block_tables.stride(1) != 1:
@@ -189,13 +267,15 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
         if isinstance(query_scale, (int, float)):
             q_scale_t, q_mode = _scalar_on_device(float(query_scale), dev), _lib.PA_QUANT_PER_TENSOR
         else:
-            _require(isinstance(query_scale, torch.Tensor) and query_scale.dtype == torch.float32,
-                     f"query_scale tensor only support dtype == torch.float32, but got query_scale.dtype == {getattr(query_scale, 'dtype', None)}")
+            if not (isinstance(query_scale, torch.Tensor) and query_scale.dtype == torch.float32):
+                _fail(f"query_scale tensor only support dtype == torch.float32, but got query_scale.dtype == {getattr(query_scale, 'dtype', None)}")
             if query_scale.dim() == 0:
                 q_scale_t, q_mode = query_scale, _lib.PA_QUANT_PER_TENSOR
             else:
-                _require(query_scale.dim() == 3, f"Expected 3D query_scale tensor, but got shape {tuple(query_scale.shape)}")
-                _require(query_scale.shape[-1] == 1, f"Expected query_scale.shape[-1] == 1, but got query_scale.shape[-1]={query_scale.shape[-1]}")
+                if not (query_scale.dim() == 3):
+                    _fail(f"Expected 3D query_scale tensor, but got shape {tuple(query_scale.shape)}")
+                if not (query_scale.shape[-1] == 1):
+                    _fail(f"Expected query_scale.shape[-1] == 1, but got query_scale.shape[-1]={query_scale.shape[-1]}")
                 q_scale_t = query_scale if query_scale.stride(1) == 1 else query_scale.contiguous()
                 q_mode, q_scale_stride = _lib.PA_QUANT_PER_TOKEN, q_scale_t.stride(0)
     k_scale_t, kv_mode = None, _lib.PA_QUANT_NONE
@@ -203,14 +283,13 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
     if key_scale is not None and value_scale is not None:
         k_scale_t, kv_mode = _kv_scale(key_scale, value_scale, "key_scale", dev)
         v_scale_t, v_mode = _kv_scale(value_scale, key_scale, "value_scale", dev)
-        _require(kv_mode == v_mode and tuple(k_scale_t.shape) == tuple(v_scale_t.shape),
-                 f"Key and value scales must have same shape, but got key: {tuple(k_scale_t.shape)}, value: {tuple(v_scale_t.shape)}")
+        if not (kv_mode == v_mode and tuple(k_scale_t.shape) == tuple(v_scale_t.shape)):
+            _fail(f"Key and value scales must have same shape, but got key: {tuple(k_scale_t.shape)}, value: {tuple(v_scale_t.shape)}")
         if kv_mode == _lib.PA_QUANT_PER_TOKEN:
-            _require(tuple(k_scale_t.shape[:3]) == (num_blocks, num_kv_heads, kv_block_size),
-                     "per-token kv scales must be [num_blocks, num_kv_heads, block_size, 1]")
-            _require(k_scale_t.stride(2) == 1 and v_scale_t.stride(2) == 1 and
-                     k_scale_t.stride() == v_scale_t.stride(),
-                     "per-token kv scales must be contiguous along block_size and share strides")
+            if not (tuple(k_scale_t.shape[:3]) == (num_blocks, num_kv_heads, kv_block_size)):
+                _fail("per-token kv scales must be [num_blocks, num_kv_heads, block_size, 1]")
+            if not (k_scale_t.stride(2) == 1 and v_scale_t.stride(2) == 1 and k_scale_t.stride() == v_scale_t.stride()):
+                _fail("per-token kv scales must be contiguous along block_size and share strides")
 
     # ---- workspaces
     max_partitions = max(1, (int(max_sequence_length) + partition_size - 1) // partition_size)
@@ -221,14 +300,12 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
         tmp_output = ws[2] if tmp_output is None else tmp_output
     ws_shape = (num_seqs, num_kv_heads, max_partitions, eq_group)
     for name, t, dt in (("exp_sums", exp_sums, torch.float32), ("max_logits", max_logits, torch.float32)):
-        _require(t.dtype == dt and t.dim() == 4 and t.shape[0] == num_seqs and t.shape[1] == num_kv_heads
-                 and t.shape[2] >= max_partitions and t.shape[3] == eq_group and t.stride(3) == 1 and t.device == dev,
-                 f"{name} must be fp32 [num_seqs, num_kv_heads, >=max_partitions, eq_group] = {ws_shape}")
-    _require(exp_sums.stride() == max_logits.stride(), "exp_sums and max_logits must share strides")
-    _require(tmp_output.dtype == output.dtype and tmp_output.dim() == 5 and tuple(tmp_output.shape[:2]) == ws_shape[:2]
-             and tmp_output.shape[2] >= max_partitions and tuple(tmp_output.shape[3:]) == (eq_group, head_size)
-             and tmp_output.stride(4) == 1 and tmp_output.device == dev,
-             f"tmp_output must be {output.dtype} {ws_shape + (head_size,)}")
+        if not (t.dtype == dt and t.dim() == 4 and t.shape[0] == num_seqs and t.shape[1] == num_kv_heads and t.shape[2] >= max_partitions and t.shape[3] == eq_group and t.stride(3) == 1 and t.device == dev):
+            _fail(f"{name} must be fp32 [num_seqs, num_kv_heads, >=max_partitions, eq_group] = {ws_shape}")
+    if not (exp_sums.stride() == max_logits.stride()):
+        _fail("exp_sums and max_logits must share strides")
+    if not (tmp_output.dtype == output.dtype and tmp_output.dim() == 5 and tuple(tmp_output.shape[:2]) == ws_shape[:2] and tmp_output.shape[2] >= max_partitions and tuple(tmp_output.shape[3:]) == (eq_group, head_size) and tmp_output.stride(4) == 1 and tmp_output.device == dev):
+        _fail(f"tmp_output must be {output.dtype} {ws_shape + (head_size,)}")
 
     p = PaDecodeParams()
     p.struct_size = C.sizeof(PaDecodeParams)
@@ -267,7 +344,11 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
         p.tune_ctas = int(tune.get("ctas", 0))
     keep = (output, query, key_cache, value_cache, sequence_lengths, block_tables, q_scale_t, k_scale_t,
             v_scale_t, alibi_slopes, exp_sums, max_logits, tmp_output, status)
-    return p, keep
+    # copies made above (contiguous query, device scalars for Python-float scales) belong to this call
+    used = (query, sequence_lengths, block_tables, q_scale_t, k_scale_t, v_scale_t)
+    cacheable = all(u is g or (isinstance(u, torch.Tensor) and isinstance(g, torch.Tensor)
+                               and u.data_ptr() == g.data_ptr()) for u, g in zip(used, given))
+    return p, keep, cacheable
 
 
 def paged_attention_decode(
