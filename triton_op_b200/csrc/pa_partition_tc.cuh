@@ -106,7 +106,8 @@ constexpr int kOffRedSum = 2048;                  // [4 groups][2 parities][16 q
 constexpr int kOffMFin = 4096;                    // [4 groups][2 parities][16] floats (max, log2 domain)
 constexpr int kOffVMax = 4608;                    // [4 groups][4 warps] floats (per-token V scale max)
 constexpr int kOffVNorm = 4672;                   // [4 groups][2 parities] floats
-constexpr int kHeadBytes = 4736;
+constexpr int kOffFRow = 4736;                    // [4 groups][2 parities][16] floats: V scale / row sum
+constexpr int kHeadBytes = 5248;
 
 // One work item: a 256-token partition of one kv head, and one block of query rows.
 struct TcItem {
@@ -204,6 +205,44 @@ __device__ __forceinline__ float warp_sum4(const float (&v)[4], int lane) {
   return c;
 }
 
+// The same exchanges with a maximum: lane ends up with the maximum for q = (lane >> 2) & 7.
+__device__ __forceinline__ float warp_max8(const float (&v)[8], int lane) {
+  const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+  float a[4], b[2];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float mine = b4 ? v[4 + j] : v[j];
+    const float other = b4 ? v[j] : v[4 + j];
+    a[j] = fmaxf(mine, __shfl_xor_sync(kFullMask, other, 16));
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float mine = b3 ? a[2 + j] : a[j];
+    const float other = b3 ? a[j] : a[2 + j];
+    b[j] = fmaxf(mine, __shfl_xor_sync(kFullMask, other, 8));
+  }
+  float c = fmaxf(b2 ? b[1] : b[0], __shfl_xor_sync(kFullMask, b2 ? b[0] : b[1], 4));
+  c = fmaxf(c, __shfl_xor_sync(kFullMask, c, 2));
+  c = fmaxf(c, __shfl_xor_sync(kFullMask, c, 1));
+  return c;
+}
+// ... and for four values: lane ends up with the maximum for q = (lane >> 3) & 3.
+__device__ __forceinline__ float warp_max4(const float (&v)[4], int lane) {
+  const bool b4 = lane & 16, b3 = lane & 8;
+  float a[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float mine = b4 ? v[2 + j] : v[j];
+    const float other = b4 ? v[j] : v[2 + j];
+    a[j] = fmaxf(mine, __shfl_xor_sync(kFullMask, other, 16));
+  }
+  float c = fmaxf(b3 ? a[1] : a[0], __shfl_xor_sync(kFullMask, b3 ? a[0] : a[1], 8));
+  c = fmaxf(c, __shfl_xor_sync(kFullMask, c, 4));
+  c = fmaxf(c, __shfl_xor_sync(kFullMask, c, 2));
+  c = fmaxf(c, __shfl_xor_sync(kFullMask, c, 1));
+  return c;
+}
+
 // ---- geometry that depends on the page size (BS = 16, 64 or 1024) -------------------------------
 template <int BS>
 struct Geo {
@@ -271,6 +310,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   float* m_fin = reinterpret_cast<float*>(smem + kOffMFin);
   float* v_max = reinterpret_cast<float*>(smem + kOffVMax);
   float* v_norm = reinterpret_cast<float*>(smem + kOffVNorm);
+  float* f_row = reinterpret_cast<float*>(smem + kOffFRow);
   const uint32_t q_ring = sbase + p.off_q;     // NSK x kQSlotBytes
   const uint32_t p_tiles = sbase + p.off_p;    // NG x kPTile
   const uint32_t k_ring = sbase + p.off_ring;  // NSK x kHalfSlot
@@ -291,7 +331,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     fence_proxy_async();
   }
   // row r = t * G + g of a kv head sees token j iff j < ctx - (L - 1 - t)
-  for (int r = tid; r < 64; r += kThreads) row_lim[r] = r < p.eqG ? (p.L - 1 - r / p.G) : -1;
+  // (padding rows of the last row block see nothing)
+  for (int r = tid; r < 64; r += kThreads) row_lim[r] = r < p.eqG ? (p.L - 1 - r / p.G) : 0x7fffffff;
   if (warp == kWarpMma) tmem_alloc(sbase + kOffTmemPtr, tmem_cols(QR));
   const int n_sp = build_partition_index(p, seq_off, seq_ctx, reinterpret_cast<int*>(smem + kOffScan));
   fence_before_sync();
@@ -663,10 +704,11 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       // orders the producer's scale writes before the reads below.
       if (!wait(bar(kBarKQFull, slot), use & 1)) return false;
       const uint32_t aux = q_ring + slot * kQSlotBytes + kQTile;
-      // per-row constants of one chunk of rows; with several chunks they are fetched again for
-      // every chunk (the chunk loops are rolled), so the query slot is released after pass 2
+      // Per-row constants of one chunk of rows (fetched again for every chunk: the chunk loops
+      // are rolled): the positive factor that turns a raw product into a base-2 logit, and the
+      // causal limit.  The query slot is released when pass 2 has read them for the last time.
       float row_scale[RC];
-      int lim[RC];  // row q sees token j iff j < ctx - lim[q]; negative: padding row, sees nothing
+      int lim[RC];  // row q sees token j iff (tokens from j to the end of the context) > lim[q]
       auto load_row_consts = [&](int ch) {
 #pragma unroll
         for (int q4 = 0; q4 < RC; q4 += 4) {
@@ -675,7 +717,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           const uint32_t w[4] = {a.x, a.y, a.z, a.w}, li[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            row_scale[q4 + e] = __uint_as_float(w[e]) * base_scale;
+            // > 0 always, so that a masked -inf stays -inf and maxima commute with the factor
+            row_scale[q4 + e] = fmaxf(__uint_as_float(w[e]) * base_scale, 1e-30f);
             lim[q4 + e] = (int)li[e];
           }
         }
@@ -689,10 +732,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           vs_tok[tg] = __uint_as_float(lds32(aux + 64 + kItemTokens * 4 + tok[tg] * 4));
         }
       }
-      if (NCH == 1) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(kBarQEmpty, slot));
-      }
       fence_after_sync();
       if (wq == 0) stamp(6, i, 0);
 
@@ -701,8 +740,10 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (room[0] <= 0) vs_tok[0] = 0.f;
         if (room[1] <= 0) vs_tok[1] = 0.f;
       }
-      // scaled, masked logits of one chunk of rows for this lane's two tokens
-      auto logits = [&](int ch, float (&s)[2][RC]) {
+      // Raw logits of one chunk of rows for this lane's two tokens: the product (times the
+      // token's key scale), -inf where the row does not see the token.  The row's factor is
+      // applied later, fused into the exponent's argument.
+      auto raw_logits = [&](int ch, float (&s)[2][RC]) {
         uint32_t h[2][8], l[2][8];
         load_rows(tmem_grp, ch, h[0], l[0]);
         load_rows(tmem_grp + N, ch, h[1], l[1]);
@@ -712,25 +753,27 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         for (int tg = 0; tg < 2; ++tg) {
 #pragma unroll
           for (int q = 0; q < RC; ++q) {
-            float v = row_value(h[tg], l[tg], q) * row_scale[q];
+            float v = row_value(h[tg], l[tg], q);
             if (PER_TOKEN) v *= ks_tok[tg];
-            s[tg][q] = (room[tg] > lim[q] && lim[q] >= 0) ? v : -INFINITY;
+            s[tg][q] = room[tg] > lim[q] ? v : -INFINITY;
           }
         }
       };
 
-      // ---- pass 1: partition maximum per row (integer warp reduction on order-preserving keys)
+      // ---- pass 1: partition maximum of the raw logits per row (transposing shuffle reduction)
       float s_keep[2][RC];
 #pragma unroll 1
       for (int ch = 0; ch < NCH; ++ch) {
-        logits(ch, s_keep);
-        int key[RC];
+        raw_logits(ch, s_keep);
+        float mx[RC];
 #pragma unroll
-        for (int q = 0; q < RC; ++q)
-          key[q] = __reduce_max_sync(kFullMask, float_to_ordered(fmaxf(s_keep[0][q], s_keep[1][q])));
-        if (lane == 0) {
-#pragma unroll
-          for (int q = 0; q < RC; ++q) rm[(ch * RC + q) * 4 + wq] = ordered_to_float(key[q]);
+        for (int q = 0; q < RC; ++q) mx[q] = fmaxf(s_keep[0][q], s_keep[1][q]);
+        if constexpr (RC == 8) {
+          const float wm = warp_max8(mx, lane);
+          if ((lane & 3) == 0) rm[(ch * 8 + ((lane >> 2) & 7)) * 4 + wq] = wm;
+        } else {
+          const float wm = warp_max4(mx, lane);
+          if ((lane & 7) == 0) rm[((lane >> 3) & 3) * 4 + wq] = wm;
         }
       }
       if (PER_TOKEN) {
@@ -744,6 +787,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         const float4 vm4 = *reinterpret_cast<const float4*>(v_max + grp * 4);
         vnorm = fmaxf(fmaxf(vm4.x, vm4.y), fmaxf(vm4.z, vm4.w));
         vinv = vnorm > 0.f ? 1.0f / vnorm : 0.f;
+        vs_tok[0] *= vinv;
+        vs_tok[1] *= vinv;
       }
       // The group's P^T tile is still being read by P.V of the group's previous item until that
       // product's commit has arrived (normally long ago).
@@ -753,7 +798,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       }
 
       if (wq == 0) stamp(6, i, 2);
-      // ---- pass 2: P = exp2(s - m) * 256, split into hi / lo e4m3, stored as P^T
+      // ---- pass 2: P = exp2(raw * factor - m) * 256, split into hi / lo e4m3, stored as P^T
       // row sums of one chunk: lane ends up with the sum of one row over the warp's 64 tokens
       auto row_sums = [&](int ch, const float (&psum)[RC]) {
         if constexpr (RC == 8) {
@@ -767,21 +812,20 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       float psum[RC];
 #pragma unroll 1
       for (int ch = 0; ch < NCH; ++ch) {
-        if (NCH > 1) logits(ch, s_keep);  // recomputed rather than kept: registers
+        if (NCH > 1) raw_logits(ch, s_keep);  // recomputed rather than kept: registers
         uint32_t pbytes[2][2 * ((RC + 3) / 4)];  // [tg][hi words, lo words], row q = byte q % 4
         float hi[2][RC], lo[2][RC];
 #pragma unroll
         for (int q = 0; q < RC; ++q) {
-          const int row = ch * RC + q;
-          const float4 m4 = *reinterpret_cast<const float4*>(rm + row * 4);
+          const float4 m4 = *reinterpret_cast<const float4*>(rm + (ch * RC + q) * 4);
           const float m = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w));
-          const float m_use = (m == -INFINITY) ? 0.f : m;
-          if (r == row) m_fin[par * 16 + row] = m;
-          const float p0 = ex2(s_keep[0][q] - m_use + 8.0f);
-          const float p1 = ex2(s_keep[1][q] - m_use + 8.0f);
+          // exponent argument raw * factor - m * factor + 8 as one multiply-add per element
+          const float off = (m == -INFINITY) ? 8.0f : fmaf(-m, row_scale[q], 8.0f);
+          const float p0 = ex2(fmaf(s_keep[0][q], row_scale[q], off));
+          const float p1 = ex2(fmaf(s_keep[1][q], row_scale[q], off));
           psum[q] = p0 + p1;
-          split_hi_lo(PER_TOKEN ? p0 * (vs_tok[0] * vinv) : p0, hi[0][q], lo[0][q]);
-          split_hi_lo(PER_TOKEN ? p1 * (vs_tok[1] * vinv) : p1, hi[1][q], lo[1][q]);
+          split_hi_lo(PER_TOKEN ? p0 * vs_tok[0] : p0, hi[0][q], lo[0][q]);
+          split_hi_lo(PER_TOKEN ? p1 * vs_tok[1] : p1, hi[1][q], lo[1][q]);
         }
         constexpr int W = (RC + 3) / 4;
         // tile rows: hi half at row ch * RC + q, lo half at row QR + ch * RC + q
@@ -802,10 +846,15 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         }
         if (NCH > 1) row_sums(ch, psum);
       }
-      if (NCH > 1) {  // the query slot's scales were read until here
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(kBarQEmpty, slot));
+      // thread `row` of the group keeps the row's maximum (base-2 logit domain) for the epilogue
+      if (r < QR) {
+        const float4 m4 = *reinterpret_cast<const float4*>(rm + r * 4);
+        const float m = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w));
+        const float sc = fmaxf(__uint_as_float(lds32(aux + r * 4)) * base_scale, 1e-30f);
+        m_fin[par * 16 + r] = (m == -INFINITY) ? m : m * sc;
       }
+      __syncwarp();   // the query slot's scales were read until here
+      if (lane == 0) mbar_arrive(bar(kBarQEmpty, slot));
       if (PER_TOKEN && r == 0) v_norm[par] = vnorm;
       if (wq == 0) stamp(6, i, 3);
 
@@ -863,14 +912,20 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       fence_after_sync();
       const float vfin = PER_TOKEN ? v_norm[par] : v_scale_t;
       const int rows = min(QR, p.eqG - it.rb * QR);   // valid rows of this block
-      // thread `row` of the group stores the row's partition maximum and exponential sum
-      if (r < rows) {
-        const int64_t ws = (int64_t)it.seq * p.ws_stride_seq + (int64_t)it.head * p.ws_stride_head +
-                           (int64_t)it.part * p.ws_stride_part + it.rb * QR + r;
+      // thread `row` of the group: the row's sum, the factor of its O^T values, and the row's
+      // partition maximum and exponential sum for the workspaces
+      if (r < QR) {
         const float4 l4 = *reinterpret_cast<const float4*>(rs + r * 4);
-        p.max_logits[ws] = m_fin[par * 16 + r] * kLn2;
-        p.exp_sums[ws] = ((l4.x + l4.y) + (l4.z + l4.w)) * (1.0f / 256.0f);
+        const float lsum = (l4.x + l4.y) + (l4.z + l4.w);   // in units of 1/256
+        f_row[par * 16 + r] = lsum > 0.f ? __fdividef(vfin, lsum) : 0.f;
+        if (r < rows) {
+          const int64_t ws = (int64_t)it.seq * p.ws_stride_seq + (int64_t)it.head * p.ws_stride_head +
+                             (int64_t)it.part * p.ws_stride_part + it.rb * QR + r;
+          p.max_logits[ws] = m_fin[par * 16 + r] * kLn2;
+          p.exp_sums[ws] = lsum * (1.0f / 256.0f);
+        }
       }
+      named_barrier_sync(bar_b, 128);
       // lane r holds head dim r of every row: 2-byte stores, 64 contiguous bytes per warp and row
       unsigned short* dst = reinterpret_cast<unsigned short*>(p.tmp_out) + (int64_t)it.seq * p.tmp_stride_seq +
                             (int64_t)it.head * p.tmp_stride_head + (int64_t)it.part * p.tmp_stride_part +
@@ -881,16 +936,18 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       for (int ch = 0; ch < NCH; ++ch) {
         uint32_t h[8], l[8];
         load_rows(otile, ch, h, l);
+        float f[RC];
+#pragma unroll
+        for (int q4 = 0; q4 < RC; q4 += 4) {
+          const float4 f4 = *reinterpret_cast<const float4*>(f_row + par * 16 + ch * RC + q4);
+          f[q4] = f4.x, f[q4 + 1] = f4.y, f[q4 + 2] = f4.z, f[q4 + 3] = f4.w;
+        }
         tmem_ld_wait();
         if (wq == 0) stamp(7, j, 2 * ch);
 #pragma unroll
         for (int q = 0; q < RC; ++q) {
-          const int row = ch * RC + q;
-          const float4 l4 = *reinterpret_cast<const float4*>(rs + row * 4);
-          const float lsum = (l4.x + l4.y) + (l4.z + l4.w);   // in units of 1/256
-          const float f = lsum > 0.f ? __fdividef(vfin, lsum) : 0.f;
-          const float o = row_value(h, l, q) * f;
-          if (row < rows) *dst = (unsigned short)(pack_bf16x2(o, 0.f) & 0xffffu);
+          const float o = row_value(h, l, q) * f[q];
+          if (ch * RC + q < rows) *dst = (unsigned short)(pack_bf16x2(o, 0.f) & 0xffffu);
           dst += row_stride;
         }
         if (wq == 0) stamp(7, j, 2 * ch + 1);
