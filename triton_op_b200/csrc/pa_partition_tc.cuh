@@ -37,7 +37,9 @@
 //                and owns its own S^T / O^T columns and P^T tile, so the per-item latency chain
 //                of a group overlaps the chains of the other groups.
 //   warp 12      tcgen05.mma issue (one elected lane) and TMEM allocation
-//   warp 13/14   K / V producers (bulk copies; page ids prefetched an item ahead)
+//   warp 13/14   K / V producers (bulk copies; page ids prefetched an item ahead).  Issuing a bulk
+//                copy costs a warp 75-90 cycles and the copies of one warp go out one after the
+//                other, so the 16 + 16 copies of an item need two warps.
 //   warp 15      query producer: bf16 -> hi/lo e4m3 tile in the B-operand layout, per-token scales
 // K and V have their own rings of 32 KB slots.  Every wait is bounded and reports
 // PA_DEV_WAIT_TIMEOUT.
@@ -60,6 +62,9 @@ constexpr int kNG = 3;                              // softmax groups
 constexpr int kLag = kNG - 1;                       // P.V trails QK^T by this many items in the issue loop
 constexpr int kThreads = (4 * kNG + 4) * 32;
 constexpr int kMaxSlots = 4;
+// The query ring has its own depth and barriers (a slot is a few KB, so the producer may run
+// further ahead than the 32 KB K slots allow).
+constexpr int kQSlots = 4;
 constexpr int kWarpMma = 4 * kNG, kWarpK = 4 * kNG + 1, kWarpV = 4 * kNG + 2, kWarpQ = 4 * kNG + 3;
 
 // ---- geometry that depends on the rows per work item (QR = 4, 8 or 16) ---------------------------
@@ -85,14 +90,15 @@ __host__ __device__ constexpr int tmem_cols(int qr) { return 4 * mma_n(qr) * kNG
 // so every barrier below is waited on either by one role in item order, or by a role that has
 // first observed an event implying the previous phase (noted at the wait).
 enum : int {
-  kBarKQFull = 0,   // [K slot] K bytes landed (transaction count) + query tile written: 2 arrivals
+  kBarKFull = 0,    // [K slot] K bytes landed (transaction count)
   kBarVFull = 4,    // [V slot] V bytes landed
-  kBarQEmpty = 8,   // [K slot] the softmax group has read the slot's scales: 4 arrivals
+  kBarQEmpty = 8,   // [query slot] the softmax group has read the slot's scales: 4 arrivals
   kBarSFull = 12,   // [group] QK^T of the group's current item is complete (commit); this also
                     //         frees the item's K slot and query tile
   kBarPFull = 16,   // [group] P^T stored, V cleared where needed, S^T consumed: 4 arrivals
   kBarOFull = 20,   // [group][parity] P.V complete (commit); this also frees the item's V slot
-  kNumBars = 28
+  kBarQFull = 28,   // [query slot] query tile (and per-token scales) written
+  kNumBars = 32
 };
 // fixed head of the shared-memory carve (bytes).  A softmax group keeps two items in flight (the
 // softmax of its next item runs before the epilogue of the previous one), so what the epilogue
@@ -311,14 +317,15 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   float* v_max = reinterpret_cast<float*>(smem + kOffVMax);
   float* v_norm = reinterpret_cast<float*>(smem + kOffVNorm);
   float* f_row = reinterpret_cast<float*>(smem + kOffFRow);
-  const uint32_t q_ring = sbase + p.off_q;     // NSK x kQSlotBytes
+  const uint32_t q_ring = sbase + p.off_q;     // kQSlots x kQSlotBytes
   const uint32_t p_tiles = sbase + p.off_p;    // NG x kPTile
   const uint32_t k_ring = sbase + p.off_ring;  // NSK x kHalfSlot
   const uint32_t v_ring = sbase + p.off_vring; // NSV x kHalfSlot
 
   if (tid == 0) {
     for (int s = 0; s < kMaxSlots; ++s) {
-      mbar_init(bar(kBarKQFull, s), 2);
+      mbar_init(bar(kBarKFull, s), 1);
+      mbar_init(bar(kBarQFull, s), 1);
       mbar_init(bar(kBarVFull, s), 1);
       mbar_init(bar(kBarQEmpty, s), 4);
     }
@@ -423,7 +430,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (!ok) { fail(); break; }
       }
       stamp(is_v ? 1 : 0, i, 1);
-      const uint32_t full = bar(is_v ? kBarVFull : kBarKQFull, slot);
+      const uint32_t full = bar(is_v ? kBarVFull : kBarKFull, slot);
       const uint32_t dst = ring + slot * kHalfSlot;
       const int npg = pages_of(it);
       const uint8_t* src = cache + (int64_t)pid * stride_block + (int64_t)it.head * stride_head;
@@ -527,8 +534,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           pid_next2 = load_page_id(it_next2);
         }
       }
-      const int slot = i % NSK;
-      const uint32_t use = (uint32_t)(i / NSK);
+      const int slot = i % kQSlots;
+      const uint32_t use = (uint32_t)(i / kQSlots);
       stamp(2, i, 0);
       if (!wait(bar(kBarQEmpty, slot), (use & 1) ^ 1)) { fail(); break; }
       stamp(2, i, 1);
@@ -596,7 +603,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       }
       fence_proxy_async();  // the tile is read by the tensor core (async proxy)
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(kBarKQFull, slot));
+      if (lane == 0) mbar_arrive(bar(kBarQFull, slot));
       stamp(2, i, 2);
     }
   } else if (warp == kWarpMma) {
@@ -613,11 +620,13 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         const int slot = i % NSK, g = i % NG;
         const uint32_t use = (uint32_t)(i / NSK);
         stamp(3, i, 0);
-        if (!wait(bar(kBarKQFull, slot), use & 1)) { fail(); break; }
+        const int qslot = i % kQSlots;
+        if (!wait(bar(kBarKFull, slot), use & 1) ||
+            !wait(bar(kBarQFull, qslot), (uint32_t)(i / kQSlots) & 1)) { fail(); break; }
         stamp(3, i, 1);
         fence_after_sync();
         const uint64_t kd = smem_desc(k_ring + slot * kHalfSlot, G::kKLbo, G::kKSbo);
-        const uint64_t qd = smem_desc(q_ring + slot * kQSlotBytes, 128, 1024);
+        const uint64_t qd = smem_desc(q_ring + qslot * kQSlotBytes, 128, 1024);
         const uint32_t d0 = tmem_base + g * 4 * N;
 #pragma unroll
         for (int tg = 0; tg < 2; ++tg) {
@@ -694,15 +703,15 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     };
 
     auto softmax = [&](int i, const TcItem& it) -> bool {
-      const int slot = i % NSK;
-      const uint32_t use = (uint32_t)(i / NSK), gu = (uint32_t)(i / NG);
+      const int slot = i % kQSlots;
+      const uint32_t use = (uint32_t)(i / kQSlots), gu = (uint32_t)(i / NG);
       const int par = grp * 2 + (int)(gu & 1);  // double-buffer index of what the epilogue reads
       if (wq == 0) stamp(4, i, 0);
       if (!wait(bar(kBarSFull, grp), gu & 1)) return false;
       if (wq == 0) stamp(4, i, 1);
       // QK^T of the item is done, so its query tile was complete: this wait returns at once and
       // orders the producer's scale writes before the reads below.
-      if (!wait(bar(kBarKQFull, slot), use & 1)) return false;
+      if (!wait(bar(kBarQFull, slot), use & 1)) return false;
       const uint32_t aux = q_ring + slot * kQSlotBytes + kQTile;
       // Per-row constants of one chunk of rows (fetched again for every chunk: the chunk loops
       // are rolled): the positive factor that turns a raw product into a base-2 logit, and the
