@@ -50,6 +50,7 @@
 #include "pa_partition_fp8.cuh"  // build_partition_index, kPageBytes
 #include "pa_tcgen05.cuh"
 
+#include <type_traits>
 #include <cuda.h>  // CUtensorMap (type only; the encoder is looked up at run time by the host code)
 #include "../../include/pa_decode_sm100.h"
 
@@ -71,9 +72,14 @@ constexpr int kWarpMma = 4 * kNG, kWarpK = 4 * kNG + 1, kWarpV = 4 * kNG + 2, kW
 // Row q of the item sits in tile row / TMEM column q (hi half) and QR + q (lo half).
 __host__ __device__ constexpr int mma_n(int qr) { return qr <= 8 ? 16 : 2 * qr; }
 __host__ __device__ constexpr int q_tile_bytes(int qr) { return mma_n(qr) * kD; }  // [row block][8 chunks][8 rows][16 B]
-// Query slot: the tile, 16 floats of per-row scales, and (per-token mode) 2 x 256 token scales.
+// Query slot.  Its first part belongs to a query TILE (the tile and 16 floats of per-row scales),
+// the rest to a work ITEM (16-byte header: which slot holds the item's tile; in per-token mode
+// 2 x 256 token scales).  Consecutive items with the same query rows share a tile, so the two
+// parts are used as two rings with their own counters.
+constexpr int kQHdr = 64;    // offset of the item header behind the tile
+constexpr int kQTok = 80;    // offset of the token scales behind the tile
 __host__ __device__ constexpr int q_slot_bytes(int qr, bool per_token) {
-  return q_tile_bytes(qr) + 64 + (per_token ? 2 * kItemTokens * 4 : 0);
+  return q_tile_bytes(qr) + kQTok + (per_token ? 2 * kItemTokens * 4 : 0);
 }
 // P^T tile of one item: 8 k-steps x [row blocks of 8][2 K units][8 rows][16 tokens].  The strides
 // are padded off the 128-byte grid (k-step stride = 48 mod 128) so that byte stores of one warp
@@ -156,6 +162,59 @@ struct ItemCursor {
     it.head = hr / p.num_row_blocks;
     it.rb = hr - it.head * p.num_row_blocks;
     it.part = sp - seq_off[seq];
+    it.ctx = seq_ctx[seq];
+    it.tok0 = it.part * kItemTokens;
+    it.ntok = min(kItemTokens, it.ctx - it.tok0);
+    return it;
+  }
+};
+
+// The other numbering: (sequence, kv head, partition, row block) with the row block fastest, for
+// CTAs that take a contiguous range of items.  Consecutive items of a CTA then mostly share
+// their query rows, so the query tile is built once per (sequence, kv head, row block) instead of
+// once per item, and the row blocks of one partition find its KV bytes in L2.  (With items
+// dealt round-robin in the first numbering the eight heads of a page are read by neighbouring
+// CTAs at about the same time, which DRAM likes better: 5 % on the 4-row benchmark shape.  The
+// contiguous form is for 16-row items, where building the query tile is what limits a CTA.)
+struct RangeCursor {
+  int seq, head, part, rb, parts, step;
+  __device__ __forceinline__ void init(int k, int step_, const KernelParams& p, const int* seq_off) {
+    step = step_;
+    const int nrb = p.num_row_blocks;
+    const int kk = k / nrb;                 // (sequence, head, partition) index
+    rb = k - kk * nrb;
+    int lo = 0, hi = p.S;                   // last sequence whose first item is <= kk
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (seq_off[mid] * p.Hkv <= kk) lo = mid; else hi = mid;
+    }
+    seq = lo;
+    parts = seq_off[seq + 1] - seq_off[seq];
+    const int rem = kk - seq_off[seq] * p.Hkv;
+    head = parts > 0 ? rem / parts : 0;
+    part = rem - head * parts;
+  }
+  __device__ __forceinline__ void advance(const KernelParams& p, const int* seq_off) {
+    for (int s = 0; s < step; ++s) {
+      if (++rb < p.num_row_blocks) continue;
+      rb = 0;
+      if (++part < parts) continue;
+      part = 0;
+      if (++head < p.Hkv) continue;
+      head = 0;
+      do {   // next sequence that has partitions (stepping past the last item leaves a state nobody reads)
+        if (seq >= p.S - 1) break;
+        ++seq;
+        parts = seq_off[seq + 1] - seq_off[seq];
+      } while (parts == 0);
+    }
+  }
+  __device__ __forceinline__ TcItem item(const KernelParams& p, const int* seq_off, const int* seq_ctx) const {
+    TcItem it;
+    it.seq = seq;
+    it.head = head;
+    it.rb = rb;
+    it.part = part;
     it.ctx = seq_ctx[seq];
     it.tok0 = it.part * kItemTokens;
     it.ntok = min(kItemTokens, it.ctx - it.tok0);
@@ -349,9 +408,13 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + kOffTmemPtr);
 
   const int n_items = n_sp * p.Hkv * p.num_row_blocks;
-  const int first = blockIdx.x;
-  const int stride = gridDim.x;
-  const int n_local = first < n_items ? (n_items - first + stride - 1) / stride : 0;
+  // items of this CTA: a contiguous range for 16-row items, else every gridDim.x-th item
+  constexpr bool kContiguous = QR == 16;
+  using Cursor = typename std::conditional<kContiguous, RangeCursor, ItemCursor>::type;
+  const int per_cta = n_items / (int)gridDim.x, extra = n_items - per_cta * (int)gridDim.x;
+  const int first = kContiguous ? (int)blockIdx.x * per_cta + min((int)blockIdx.x, extra) : (int)blockIdx.x;
+  const int stride = kContiguous ? 1 : (int)gridDim.x;
+  const int n_local = per_cta + ((int)blockIdx.x < extra ? 1 : 0);
   bool dead = false;
 
   // Tuning aid: when p.trace is set, lane 0 of each role of CTA 0 stamps the SM clock at a few
@@ -369,9 +432,14 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     return __all_sync(kFullMask, mbar_wait(b, parity));
   };
   // block-table entry of page `pg` (counted inside the item) of an item, clamped
-  auto page_id = [&](const TcItem& it, int pg, bool report) -> int {
+  // Block-table entry of page `pg` (counted inside the item) of an item, as loaded: the roles
+  // fetch it an item ahead and must not touch the value before they use it (a comparison right
+  // after the load would make them wait for it there), so clamping is a separate step.
+  auto page_id_raw = [&](const TcItem& it, int pg) -> int {
     const int64_t col = BS >= kItemTokens ? (int64_t)(it.tok0 / BS) : (int64_t)it.part * kPagesPerItem + pg;
-    int id = __ldg(p.block_tables + (int64_t)it.seq * p.bt_stride_seq + col);
+    return __ldg(p.block_tables + (int64_t)it.seq * p.bt_stride_seq + col);
+  };
+  auto clamp_page = [&](int id, bool report) -> int {
     if ((unsigned)id >= (unsigned)p.num_blocks) {
       id = 0;
       if (report && p.status) atomicOr(p.status, PA_DEV_BAD_PAGE_ID);
@@ -398,9 +466,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     };
     auto load_page_id = [&](const TcItem& it) -> int {
       const int pg = my_page();
-      return pg < pages_of(it) ? page_id(it, pg, true) : 0;
+      return pg < pages_of(it) ? page_id_raw(it, pg) : 0;
     };
-    ItemCursor cur;
+    Cursor cur;
     TcItem it_next{};
     int pid_next = 0;
     if (n_local > 0) {
@@ -410,7 +478,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     }
     for (int i = 0; i < n_local && !dead; ++i) {
       const TcItem it = it_next;
-      const int pid = pid_next;
+      const int pid = clamp_page(pid_next, true);
       if (i + 1 < n_local) {
         cur.advance(p, seq_off);
         it_next = cur.item(p, seq_off, seq_ctx);
@@ -484,14 +552,14 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     // per-token scales: lane fetches the K and the V scales of tokens 8*lane .. 8*lane+7 of the item
     auto scale_page = [&]() -> int { return BS == 16 ? (lane >> 1) : (BS == 64 ? (lane >> 3) : 0); };
     auto load_page_id = [&](const TcItem& it) -> int {
-      return (PER_TOKEN && 8 * lane < it.ntok) ? page_id(it, scale_page(), false) : 0;
+      return (PER_TOKEN && 8 * lane < it.ntok) ? page_id_raw(it, scale_page()) : 0;
     };
     auto load_scales = [&](const TcItem& it, int pid, uint4 (&raw)[4]) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) raw[e] = make_uint4(0u, 0u, 0u, 0u);
       if (PER_TOKEN && 8 * lane < it.ntok) {
         const int off = BS == 16 ? (lane & 1) * 8 : (BS == 64 ? (lane & 7) * 8 : (it.tok0 % BS) + 8 * lane);
-        const int64_t base = (int64_t)pid * p.kvs_stride_block + (int64_t)it.head * p.kvs_stride_head + off;
+        const int64_t base = (int64_t)clamp_page(pid, false) * p.kvs_stride_block + (int64_t)it.head * p.kvs_stride_head + off;
         const uint4* ks = reinterpret_cast<const uint4*>(p.k_scale + base);
         const uint4* vs = reinterpret_cast<const uint4*>(p.v_scale + base);
         raw[0] = __ldg(ks);
@@ -500,10 +568,23 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         raw[3] = __ldg(vs + 1);
       }
     };
-    ItemCursor cur;
+    Cursor cur;
     TcItem it_next{}, it_next2{};
     uint4 q_next[kPasses][4], sc_next[4];
     int pid_next2 = 0;
+    // A tile is built when an item's query rows are not among the tiles of the current
+    // (sequence, kv head): one tile per row block, remembered until the head changes.  It goes
+    // to tile slot (tile count) % kQSlots.  That slot's previous tile is four tiles old; a
+    // (sequence, kv head) uses each of its (at most four) tiles at least once, in row-block
+    // order, so that tile's last user is at least four items back, and this loop has waited
+    // for that item's release.
+    int tile = -1;
+    int key_seq = -1, key_head = -1;
+    uint32_t tile_slots = 0;     // 4 bits per row block: bit 3 = valid, bits 0-1 = slot
+    auto have_tile = [&](const TcItem& it) -> bool {
+      return it.seq == key_seq && it.head == key_head && ((tile_slots >> (4 * it.rb)) & 8u) != 0;
+    };
+    bool fresh_next = true;
     if (n_local > 0) {
       cur.init(first, stride, p, seq_off);
       it_next = cur.item(p, seq_off, seq_ctx);
@@ -524,9 +605,21 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
 #pragma unroll
         for (int ps = 0; ps < kPasses; ++ps) qraw[ps][e] = q_next[ps][e];
       }
+      const bool fresh = fresh_next;
+      if (it.seq != key_seq || it.head != key_head) {
+        key_seq = it.seq;
+        key_head = it.head;
+        tile_slots = 0;
+      }
+      if (fresh) {
+        ++tile;
+        tile_slots = (tile_slots & ~(15u << (4 * it.rb))) | ((8u | (uint32_t)(tile % kQSlots)) << (4 * it.rb));
+      }
+      const int tslot = (int)((tile_slots >> (4 * it.rb)) & 3u);
       if (i + 1 < n_local) {
         it_next = it_next2;
-        load_q(it_next, q_next);
+        fresh_next = !have_tile(it_next);
+        if (fresh_next) load_q(it_next, q_next);
         load_scales(it_next, pid_next2, sc_next);
         if (i + 2 < n_local) {
           cur.advance(p, seq_off);
@@ -539,11 +632,13 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       stamp(2, i, 0);
       if (!wait(bar(kBarQEmpty, slot), (use & 1) ^ 1)) { fail(); break; }
       stamp(2, i, 1);
-      const uint32_t qt = q_ring + slot * kQSlotBytes;
-      const uint32_t aux = qt + kQTile;
+      const uint32_t qt = q_ring + tslot * kQSlotBytes;
+      const uint32_t aux = qt + kQTile;                                   // the tile's row scales
+      const uint32_t item_aux = q_ring + slot * kQSlotBytes + kQTile;     // the item's header and token scales
+      if (lane == 0) sts32(item_aux + kQHdr, (uint32_t)tslot);
       // (rolled: the code of every role's loop should stay resident in the instruction cache)
 #pragma unroll 1
-      for (int ps = 0; ps < kPasses; ++ps) {
+      for (int ps = 0; ps < (fresh ? kPasses : 0); ++ps) {
         const int n = ps * 8 + n0;
         const int row = it.rb * QR + n;
         // row maximum -> power-of-two pre-scale putting it in [128, 256)
@@ -596,10 +691,10 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         }
       }
       if (PER_TOKEN) {
-        sts128(aux + 64 + lane * 32, sraw[0]);
-        sts128(aux + 64 + lane * 32 + 16, sraw[1]);
-        sts128(aux + 64 + kItemTokens * 4 + lane * 32, sraw[2]);
-        sts128(aux + 64 + kItemTokens * 4 + lane * 32 + 16, sraw[3]);
+        sts128(item_aux + kQTok + lane * 32, sraw[0]);
+        sts128(item_aux + kQTok + lane * 32 + 16, sraw[1]);
+        sts128(item_aux + kQTok + kItemTokens * 4 + lane * 32, sraw[2]);
+        sts128(item_aux + kQTok + kItemTokens * 4 + lane * 32 + 16, sraw[3]);
       }
       fence_proxy_async();  // the tile is read by the tensor core (async proxy)
       __syncwarp();
@@ -626,7 +721,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         stamp(3, i, 1);
         fence_after_sync();
         const uint64_t kd = smem_desc(k_ring + slot * kHalfSlot, G::kKLbo, G::kKSbo);
-        const uint64_t qd = smem_desc(q_ring + qslot * kQSlotBytes, 128, 1024);
+        const uint32_t tslot = lds32(q_ring + qslot * kQSlotBytes + kQTile + kQHdr);  // slot of the item's tile
+        const uint64_t qd = smem_desc(q_ring + tslot * kQSlotBytes, 128, 1024);
         const uint32_t d0 = tmem_base + g * 4 * N;
 #pragma unroll
         for (int tg = 0; tg < 2; ++tg) {
@@ -712,7 +808,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       // QK^T of the item is done, so its query tile was complete: this wait returns at once and
       // orders the producer's scale writes before the reads below.
       if (!wait(bar(kBarQFull, slot), use & 1)) return false;
-      const uint32_t aux = q_ring + slot * kQSlotBytes + kQTile;
+      const uint32_t item_aux = q_ring + slot * kQSlotBytes + kQTile;   // header, token scales
+      const uint32_t aux = q_ring + lds32(item_aux + kQHdr) * kQSlotBytes + kQTile;   // the tile's row scales
       // Per-row constants of one chunk of rows (fetched again for every chunk: the chunk loops
       // are rolled): the positive factor that turns a raw product into a base-2 logit, and the
       // causal limit.  The query slot is released when pass 2 has read them for the last time.
@@ -737,8 +834,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       if (PER_TOKEN) {
 #pragma unroll
         for (int tg = 0; tg < 2; ++tg) {
-          ks_tok[tg] = __uint_as_float(lds32(aux + 64 + tok[tg] * 4));
-          vs_tok[tg] = __uint_as_float(lds32(aux + 64 + kItemTokens * 4 + tok[tg] * 4));
+          ks_tok[tg] = __uint_as_float(lds32(item_aux + kQTok + tok[tg] * 4));
+          vs_tok[tg] = __uint_as_float(lds32(item_aux + kQTok + kItemTokens * 4 + tok[tg] * 4));
         }
       }
       fence_after_sync();
@@ -968,7 +1065,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
 
     // group g walks the CTA's items g, g+NG, ...; the epilogue of an item runs after the softmax
     // of the group's next item, by which time its P.V product has long been issued
-    ItemCursor cur;
+    Cursor cur;
     if (grp < n_local) cur.init(first + grp * stride, NG * stride, p, seq_off);
     TcItem it_prev{};
     int prev = -1;
