@@ -73,13 +73,12 @@ constexpr int kWarpMma = 4 * kNG, kWarpK = 4 * kNG + 1, kWarpV = 4 * kNG + 2, kW
 __host__ __device__ constexpr int mma_n(int qr) { return qr <= 8 ? 16 : 2 * qr; }
 __host__ __device__ constexpr int q_tile_bytes(int qr) { return mma_n(qr) * kD; }  // [row block][8 chunks][8 rows][16 B]
 // Query slot.  Its first part belongs to a query TILE (the tile and 16 floats of per-row scales),
-// the rest to a work ITEM (16-byte header: which slot holds the item's tile; in per-token mode
-// 2 x 256 token scales).  Consecutive items with the same query rows share a tile, so the two
-// parts are used as two rings with their own counters.
+// the rest to a work ITEM (16-byte header: which slot holds the item's tile).  Consecutive items
+// with the same query rows share a tile, so the two parts are used as two rings with their own
+// counters.
 constexpr int kQHdr = 64;    // offset of the item header behind the tile
-constexpr int kQTok = 80;    // offset of the token scales behind the tile
-__host__ __device__ constexpr int q_slot_bytes(int qr, bool per_token) {
-  return q_tile_bytes(qr) + kQTok + (per_token ? 2 * kItemTokens * 4 : 0);
+__host__ __device__ constexpr int q_slot_bytes(int qr, bool /*per_token*/) {
+  return q_tile_bytes(qr) + kQHdr + 16;
 }
 // P^T tile of one item: 8 k-steps x [row blocks of 8][2 K units][8 rows][16 tokens].  The strides
 // are padded off the 128-byte grid (k-step stride = 48 mod 128) so that byte stores of one warp
@@ -549,29 +548,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         }
       }
     };
-    // per-token scales: lane fetches the K and the V scales of tokens 8*lane .. 8*lane+7 of the item
-    auto scale_page = [&]() -> int { return BS == 16 ? (lane >> 1) : (BS == 64 ? (lane >> 3) : 0); };
-    auto load_page_id = [&](const TcItem& it) -> int {
-      return (PER_TOKEN && 8 * lane < it.ntok) ? page_id_raw(it, scale_page()) : 0;
-    };
-    auto load_scales = [&](const TcItem& it, int pid, uint4 (&raw)[4]) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) raw[e] = make_uint4(0u, 0u, 0u, 0u);
-      if (PER_TOKEN && 8 * lane < it.ntok) {
-        const int off = BS == 16 ? (lane & 1) * 8 : (BS == 64 ? (lane & 7) * 8 : (it.tok0 % BS) + 8 * lane);
-        const int64_t base = (int64_t)clamp_page(pid, false) * p.kvs_stride_block + (int64_t)it.head * p.kvs_stride_head + off;
-        const uint4* ks = reinterpret_cast<const uint4*>(p.k_scale + base);
-        const uint4* vs = reinterpret_cast<const uint4*>(p.v_scale + base);
-        raw[0] = __ldg(ks);
-        raw[1] = __ldg(ks + 1);
-        raw[2] = __ldg(vs);
-        raw[3] = __ldg(vs + 1);
-      }
-    };
     Cursor cur;
-    TcItem it_next{}, it_next2{};
-    uint4 q_next[kPasses][4], sc_next[4];
-    int pid_next2 = 0;
+    TcItem it_next{};
+    uint4 q_next[kPasses][4];
     // A tile is built when an item's query rows are not among the tiles of the current
     // (sequence, kv head): one tile per row block, remembered until the head changes.  It goes
     // to tile slot (tile count) % kQSlots.  That slot's previous tile is four tiles old; a
@@ -589,19 +568,12 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       cur.init(first, stride, p, seq_off);
       it_next = cur.item(p, seq_off, seq_ctx);
       load_q(it_next, q_next);
-      load_scales(it_next, load_page_id(it_next), sc_next);
-      if (n_local > 1) {
-        cur.advance(p, seq_off);
-        it_next2 = cur.item(p, seq_off, seq_ctx);
-        pid_next2 = load_page_id(it_next2);
-      }
     }
     for (int i = 0; i < n_local && !dead; ++i) {
       const TcItem it = it_next;
-      uint4 qraw[kPasses][4], sraw[4];
+      uint4 qraw[kPasses][4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        sraw[e] = sc_next[e];
 #pragma unroll
         for (int ps = 0; ps < kPasses; ++ps) qraw[ps][e] = q_next[ps][e];
       }
@@ -617,15 +589,10 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       }
       const int tslot = (int)((tile_slots >> (4 * it.rb)) & 3u);
       if (i + 1 < n_local) {
-        it_next = it_next2;
+        cur.advance(p, seq_off);
+        it_next = cur.item(p, seq_off, seq_ctx);
         fresh_next = !have_tile(it_next);
         if (fresh_next) load_q(it_next, q_next);
-        load_scales(it_next, pid_next2, sc_next);
-        if (i + 2 < n_local) {
-          cur.advance(p, seq_off);
-          it_next2 = cur.item(p, seq_off, seq_ctx);
-          pid_next2 = load_page_id(it_next2);
-        }
       }
       const int slot = i % kQSlots;
       const uint32_t use = (uint32_t)(i / kQSlots);
@@ -634,7 +601,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       stamp(2, i, 1);
       const uint32_t qt = q_ring + tslot * kQSlotBytes;
       const uint32_t aux = qt + kQTile;                                   // the tile's row scales
-      const uint32_t item_aux = q_ring + slot * kQSlotBytes + kQTile;     // the item's header and token scales
+      const uint32_t item_aux = q_ring + slot * kQSlotBytes + kQTile;     // the item's header
       if (lane == 0) sts32(item_aux + kQHdr, (uint32_t)tslot);
       // (rolled: the code of every role's loop should stay resident in the instruction cache)
 #pragma unroll 1
@@ -689,12 +656,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
             qs = __ldg(p.q_scale + (int64_t)it.seq * p.q_scale_stride_seq + it.head * p.eqG + row);
           sts32(aux + n * 4, __float_as_uint(inv_pre * qs));
         }
-      }
-      if (PER_TOKEN) {
-        sts128(item_aux + kQTok + lane * 32, sraw[0]);
-        sts128(item_aux + kQTok + lane * 32 + 16, sraw[1]);
-        sts128(item_aux + kQTok + kItemTokens * 4 + lane * 32, sraw[2]);
-        sts128(item_aux + kQTok + kItemTokens * 4 + lane * 32 + 16, sraw[3]);
       }
       fence_proxy_async();  // the tile is read by the tensor core (async proxy)
       __syncwarp();
@@ -798,7 +759,40 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
                      : fmaf(__uint_as_float(l[q]), 0.0625f, __uint_as_float(h[q]));
     };
 
-    auto softmax = [&](int i, const TcItem& it) -> bool {
+    // Per-token K / V scales of this lane's two tokens come straight from global memory, fetched
+    // ahead by the group itself: the block-table entry two of the group's items ahead, the four
+    // scales one item ahead (each step has a whole group iteration to land).
+    auto load_tok_pids = [&](const TcItem& it, int (&pid)[2]) {
+      pid[0] = 0;
+      pid[1] = 0;
+      if (PER_TOKEN) {
+        // tokens of one lane share a page unless pages hold 64 tokens (then they are 128 tokens apart)
+        if (tok[0] < it.ntok) pid[0] = page_id_raw(it, BS == 16 ? (tok[0] >> 4) : (BS == 64 ? (tok[0] >> 6) : 0));
+        if (BS == 64) {
+          if (tok[1] < it.ntok) pid[1] = page_id_raw(it, tok[1] >> 6);
+        } else {
+          pid[1] = pid[0];
+        }
+      }
+    };
+    auto load_tok_scales = [&](const TcItem& it, const int (&pid)[2], float (&sc)[4]) {  // k0, k1, v0, v1
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[e] = 0.f;
+      if (PER_TOKEN) {
+#pragma unroll
+        for (int tg = 0; tg < 2; ++tg) {
+          if (tok[tg] < it.ntok) {
+            const int in_page = BS == 16 ? (tok[tg] & 15) : (BS == 64 ? (tok[tg] & 63) : (it.tok0 % BS) + tok[tg]);
+            const int64_t idx = (int64_t)clamp_page(pid[tg], false) * p.kvs_stride_block +
+                                (int64_t)it.head * p.kvs_stride_head + in_page;
+            sc[tg] = __ldg(p.k_scale + idx);
+            sc[2 + tg] = __ldg(p.v_scale + idx);
+          }
+        }
+      }
+    };
+
+    auto softmax = [&](int i, const TcItem& it, const float (&tok_scales)[4]) -> bool {
       const int slot = i % kQSlots;
       const uint32_t use = (uint32_t)(i / kQSlots), gu = (uint32_t)(i / NG);
       const int par = grp * 2 + (int)(gu & 1);  // double-buffer index of what the epilogue reads
@@ -808,7 +802,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       // QK^T of the item is done, so its query tile was complete: this wait returns at once and
       // orders the producer's scale writes before the reads below.
       if (!wait(bar(kBarQFull, slot), use & 1)) return false;
-      const uint32_t item_aux = q_ring + slot * kQSlotBytes + kQTile;   // header, token scales
+      const uint32_t item_aux = q_ring + slot * kQSlotBytes + kQTile;   // the item's header
       const uint32_t aux = q_ring + lds32(item_aux + kQHdr) * kQSlotBytes + kQTile;   // the tile's row scales
       // Per-row constants of one chunk of rows (fetched again for every chunk: the chunk loops
       // are rolled): the positive factor that turns a raw product into a base-2 logit, and the
@@ -832,11 +826,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       if (NCH == 1) load_row_consts(0);
       float ks_tok[2] = {1.f, 1.f}, vs_tok[2] = {1.f, 1.f};
       if (PER_TOKEN) {
-#pragma unroll
-        for (int tg = 0; tg < 2; ++tg) {
-          ks_tok[tg] = __uint_as_float(lds32(item_aux + kQTok + tok[tg] * 4));
-          vs_tok[tg] = __uint_as_float(lds32(item_aux + kQTok + kItemTokens * 4 + tok[tg] * 4));
-        }
+        ks_tok[0] = tok_scales[0], ks_tok[1] = tok_scales[1];
+        vs_tok[0] = tok_scales[2], vs_tok[1] = tok_scales[3];
       }
       fence_after_sync();
       if (wq == 0) stamp(6, i, 0);
@@ -1067,21 +1058,46 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     // of the group's next item, by which time its P.V product has long been issued
     Cursor cur;
     if (grp < n_local) cur.init(first + grp * stride, NG * stride, p, seq_off);
+    // the group's current item and the two after it (for the scale prefetch)
+    TcItem it0{}, it1{}, it2{};
+    int pid1[2] = {0, 0};            // block-table entries of it1's pages, in flight
+    float sc0[4] = {0.f, 0.f, 0.f, 0.f};   // token scales of it0, in flight
+    if (grp < n_local) {
+      it0 = cur.item(p, seq_off, seq_ctx);
+      if (PER_TOKEN) {
+        int pid0[2];
+        load_tok_pids(it0, pid0);
+        load_tok_scales(it0, pid0, sc0);
+      }
+    }
+    if (grp + NG < n_local) {
+      cur.advance(p, seq_off);
+      it1 = cur.item(p, seq_off, seq_ctx);
+      load_tok_pids(it1, pid1);
+    }
     TcItem it_prev{};
     int prev = -1;
     // one call site each for softmax and epilogue: the code of this loop should stay small
     for (int i = grp; !dead; i += NG) {
       const bool more = i < n_local;
-      TcItem it{};
       if (more) {
-        it = cur.item(p, seq_off, seq_ctx);
-        cur.advance(p, seq_off);
-        if (!softmax(i, it)) { fail(); break; }
+        float sc_use[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc_use[e] = sc0[e];
+        if (PER_TOKEN && i + NG < n_local) load_tok_scales(it1, pid1, sc0);
+        if (i + 2 * NG < n_local) {
+          cur.advance(p, seq_off);
+          it2 = cur.item(p, seq_off, seq_ctx);
+          load_tok_pids(it2, pid1);
+        }
+        if (!softmax(i, it0, sc_use)) { fail(); break; }
       }
       if (prev >= 0 && !epilogue(prev, it_prev, !more)) { fail(); break; }
       if (!more) break;
-      it_prev = it;
+      it_prev = it0;
       prev = i;
+      it0 = it1;
+      it1 = it2;
     }
   }
 
