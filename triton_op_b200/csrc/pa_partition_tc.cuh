@@ -132,13 +132,17 @@ struct TcItem {
 // ((sequence, partition) pair, head, row block) with the row block fastest.  Decoding an index
 // needs a search in the partition prefix sum; the cursor does that once and then steps forward.
 struct ItemCursor {
-  int sp, hr, seq, step_sp, step_hr, hr_count;
-  __device__ __forceinline__ void init(int k, int step, const KernelParams& p, const int* seq_off) {
-    hr_count = p.Hkv * p.num_row_blocks;
+  int sp, head, rb, seq, step_sp, step_head, step_rb;   // (the step is kept in the same mixed radix: no divisions per item)
+  __device__ __noinline__ void init(int k, int step, const KernelParams& p, const int* seq_off) {
+    const int nrb = p.num_row_blocks, hr_count = p.Hkv * nrb;
     sp = k / hr_count;
-    hr = k - sp * hr_count;
+    const int hr = k - sp * hr_count;
+    head = hr / nrb;
+    rb = hr - head * nrb;
     step_sp = step / hr_count;
-    step_hr = step - step_sp * hr_count;
+    const int shr = step - step_sp * hr_count;
+    step_head = shr / nrb;
+    step_rb = shr - step_head * nrb;
     int lo = 0, hi = p.S;
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
@@ -147,19 +151,24 @@ struct ItemCursor {
     seq = lo;
   }
   __device__ __forceinline__ void advance(const KernelParams& p, const int* seq_off) {
-    hr += step_hr;
-    sp += step_sp;
-    if (hr >= hr_count) {
-      hr -= hr_count;
+    rb += step_rb;
+    if (rb >= p.num_row_blocks) {
+      rb -= p.num_row_blocks;
+      ++head;
+    }
+    head += step_head;
+    if (head >= p.Hkv) {
+      head -= p.Hkv;
       ++sp;
     }
+    sp += step_sp;
     while (seq < p.S - 1 && seq_off[seq + 1] <= sp) ++seq;
   }
   __device__ __forceinline__ TcItem item(const KernelParams& p, const int* seq_off, const int* seq_ctx) const {
     TcItem it;
     it.seq = seq;
-    it.head = hr / p.num_row_blocks;
-    it.rb = hr - it.head * p.num_row_blocks;
+    it.head = head;
+    it.rb = rb;
     it.part = sp - seq_off[seq];
     it.ctx = seq_ctx[seq];
     it.tok0 = it.part * kItemTokens;
@@ -177,7 +186,7 @@ struct ItemCursor {
 // contiguous form is for 16-row items, where building the query tile is what limits a CTA.)
 struct RangeCursor {
   int seq, head, part, rb, parts, step;
-  __device__ __forceinline__ void init(int k, int step_, const KernelParams& p, const int* seq_off) {
+  __device__ __noinline__ void init(int k, int step_, const KernelParams& p, const int* seq_off) {
     step = step_;
     const int nrb = p.num_row_blocks;
     const int kk = k / nrb;                 // (sequence, head, partition) index
@@ -220,6 +229,11 @@ struct RangeCursor {
     return it;
   }
 };
+
+// Error bits are set from rare paths only: one shared out-of-line copy of the atomic.
+__device__ __noinline__ void report_status(int32_t* status, int bit) {
+  if (status) atomicOr(status, bit);
+}
 
 // Monotonic float <-> int map, so a float maximum can use the single-instruction integer
 // warp reduction.
@@ -424,7 +438,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   };
   auto fail = [&]() {
     dead = true;
-    if (lane == 0 && p.status) atomicOr(p.status, PA_DEV_WAIT_TIMEOUT);
+    if (lane == 0) report_status(p.status, PA_DEV_WAIT_TIMEOUT);
   };
   // whole-warp bounded wait, uniform result
   auto wait = [&](uint32_t b, uint32_t parity) -> bool {
@@ -441,7 +455,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   auto clamp_page = [&](int id, bool report) -> int {
     if ((unsigned)id >= (unsigned)p.num_blocks) {
       id = 0;
-      if (report && p.status) atomicOr(p.status, PA_DEV_BAD_PAGE_ID);
+      if (report) report_status(p.status, PA_DEV_BAD_PAGE_ID);
     }
     return id;
   };
@@ -608,22 +622,21 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       for (int ps = 0; ps < (fresh ? kPasses : 0); ++ps) {
         const int n = ps * 8 + n0;
         const int row = it.rb * QR + n;
-        // row maximum -> power-of-two pre-scale putting it in [128, 256)
-        float x[32];
+        uint4 qv[4];   // this lane's 32 bf16 of the row
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          uint4 qv = qraw[0][e];
-          if (kPasses > 1 && ps == 1) qv = qraw[kPasses - 1][e];
-          const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            x[e * 8 + 2 * k] = bf16_lo_to_f32(w[k]);
-            x[e * 8 + 2 * k + 1] = bf16_hi_to_f32(w[k]);
-          }
+          qv[e] = qraw[0][e];
+          if (kPasses > 1 && ps == 1) qv[e] = qraw[kPasses - 1][e];
         }
-        float amax = 0.f;
+        // row maximum -> power-of-two pre-scale putting it in [128, 256).  |x| of a packed bf16
+        // pair is a mask, and non-negative bf16 bit patterns order like unsigned integers.
+        uint32_t m2 = 0;
 #pragma unroll
-        for (int e = 0; e < 32; ++e) amax = fmaxf(amax, fabsf(x[e]));
+        for (int e = 0; e < 4; ++e) {
+          m2 = __vmaxu2(m2, __vmaxu2(__vmaxu2(qv[e].x & 0x7fff7fffu, qv[e].y & 0x7fff7fffu),
+                                     __vmaxu2(qv[e].z & 0x7fff7fffu, qv[e].w & 0x7fff7fffu)));
+        }
+        float amax = __uint_as_float(max(m2 & 0xffffu, m2 >> 16) << 16);
         amax = quad_max(amax);
         float pre = 1.0f, inv_pre = 1.0f;
         const int be = (int)((__float_as_uint(amax) >> 23) & 0xff);
@@ -631,14 +644,18 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           pre = __uint_as_float((uint32_t)(254 + 7 - be) << 23);
           inv_pre = __uint_as_float((uint32_t)(be - 7) << 23);
         }
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {  // the two 16-dim chunks of this lane's quarter
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {  // the two 16-dim chunks of this lane's quarter (rolled: code size)
+          const uint4 a = c ? qv[2] : qv[0], b = c ? qv[3] : qv[1];
+          const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
           uint32_t hi4[4], lo4[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
+            const float x[4] = {bf16_lo_to_f32(w[2 * k]), bf16_hi_to_f32(w[2 * k]),
+                                bf16_lo_to_f32(w[2 * k + 1]), bf16_hi_to_f32(w[2 * k + 1])};
             float hi[4], lo[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) split_hi_lo(x[c * 16 + k * 4 + e] * pre, hi[e], lo[e]);
+            for (int e = 0; e < 4; ++e) split_hi_lo(x[e] * pre, hi[e], lo[e]);
             hi4[k] = pack_e4m3x4(hi[0], hi[1], hi[2], hi[3]);
             lo4[k] = pack_e4m3x4(lo[0], lo[1], lo[2], lo[3]);
           }
