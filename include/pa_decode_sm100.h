@@ -132,8 +132,9 @@ typedef struct PaDecodeParams {
   float softmax_scale;
 
   /* 0 = library default.  tune_warps: consumer warps per CTA; tune_stages: ring depth per
-   * warp; tune_ctas: grid size.  For benchmarking sweeps; results do not depend on them. */
-  int32_t tune_warps, tune_stages, tune_ctas, reserved0;
+   * warp (K ring of the tcgen05 kernel); tune_vstages: V ring depth of the tcgen05 kernel;
+   * tune_ctas: grid size.  For benchmarking sweeps; results do not depend on them. */
+  int32_t tune_warps, tune_stages, tune_ctas, tune_vstages;
 } PaDecodeParams;
 
 /* Partition kernel followed by the reduce kernel on `stream` (a cudaStream_t). */

@@ -257,6 +257,7 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
     bool placed = false;
     for (const auto& d : kDepths) {
       if (p->tune_stages > 0 && d[0] > p->tune_stages && d[0] > 2) continue;
+      if (p->tune_vstages > 0 && d[1] != p->tune_vstages) continue;
       const int off_p = round_up(off + pa::tc::kQSlots * qslot, 128);
       const int ring = round_up(off_p + pa::tc::kNG * pa::tc::p_tile_bytes(qr), 1024);
       const int total = ring + (d[0] + d[1]) * pa::tc::kHalfSlot;

@@ -342,6 +342,7 @@ def _build_params(output, query, key_cache, value_cache, sequence_lengths, block
         p.tune_warps = int(tune.get("warps", 0))
         p.tune_stages = int(tune.get("stages", 0))
         p.tune_ctas = int(tune.get("ctas", 0))
+        p.tune_vstages = int(tune.get("vstages", 0))
     keep = (output, query, key_cache, value_cache, sequence_lengths, block_tables, q_scale_t, k_scale_t,
             v_scale_t, alibi_slopes, exp_sums, max_logits, tmp_output, status)
     # copies made above (contiguous query, device scalars for Python-float scales) belong to this call
