@@ -232,3 +232,38 @@ def test_long_contexts_use_the_multi_warp_reduce(lens, psize, ql):
     torch.cuda.synchronize()
     assert res["exponential_sums"].shape[2] > 32
     assert_close(out, oracle_output(inp), what=f"{lens} partition {psize}")
+
+
+@pytest.mark.parametrize("heads,ql,bs,kvq", [((32, 8), 1, 16, "per_tensor"), ((16, 2), 1, 16, "per_token"),
+                                             ((16, 2), 2, 1024, "per_token"), ((10, 1), 3, 64, "per_tensor")])
+@pytest.mark.parametrize("qmode", ["per_tensor", "per_token"])
+def test_fp8_query_with_query_scale(heads, ql, bs, kvq, qmode):
+    """e4m3fn query rows with a per-tensor or per-row query scale (the reference's fp8 entry,
+    pa_decode_triton_gluon_fp8.py:1752-1768): compared with the oracle on the dequantised rows."""
+    from oracle import pa_oracle
+    from triton_op_b200 import paged_attention_decode
+    from triton_op_b200.inputs import FP8, FP8_MAX, DecodeConfig, make_inputs, pack_mtp, unpack_mtp
+    hq, hkv = heads
+    cfg = DecodeConfig("fp8q", 3, hq, hkv, bs, ql, ("fixed", 1), quant=kvq)
+    inp = make_inputs(cfg, seed=17, device=DEV, context_lens=torch.tensor([700, 2049, 33]))
+    q = inp.query_tokens.float()                                    # [S*L, Hq, D]
+    if qmode == "per_tensor":
+        scale = (q.abs().amax() / FP8_MAX).clamp_min(1e-12)
+        scale_tok = scale
+    else:
+        scale_tok = (q.abs().amax(dim=-1, keepdim=True) / FP8_MAX).clamp_min(1e-12)   # [S*L, Hq, 1]
+        scale = pack_mtp(scale_tok.expand(-1, -1, 1).contiguous(), cfg.num_seqs, ql, hkv).contiguous()  # operator row order
+    q8_tok = (q / scale_tok).to(FP8)
+    q_deq = q8_tok.float() * scale_tok
+    q8 = pack_mtp(q8_tok.view(torch.uint8), cfg.num_seqs, ql, hkv).contiguous().view(FP8)
+    out = torch.full(q8.shape, float("nan"), dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    paged_attention_decode(out, q8, inp.key_cache, inp.value_cache, inp.context_lens, inp.block_tables,
+                           inp.softmax_scale, ql, inp.max_context, torch.bfloat16, scale, inp.key_scale,
+                           inp.value_scale, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ks, vs = inp.flat_scales()
+    ref = pa_oracle.paged_attention(q_deq, inp.key_cache, inp.value_cache, inp.block_tables, inp.context_lens,
+                                    inp.query_indptr(), ks, vs)
+    assert_close(unpack_mtp(out, cfg.num_seqs, ql, hkv), ref, what=f"fp8 query {qmode}")

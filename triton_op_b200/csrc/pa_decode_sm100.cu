@@ -144,7 +144,8 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   if (rc != PA_OK) return rc;
 
   const int eqG = p->query_group_size * p->query_len;
-  if (p->q_dtype != PA_DT_BF16) return PA_ERR_UNSUPPORTED;
+  if (p->q_dtype != PA_DT_BF16 && p->q_dtype != PA_DT_E4M3FN) return PA_ERR_UNSUPPORTED;
+  const int q_item = p->q_dtype == PA_DT_BF16 ? 2 : 1;   // bytes per query element
   if (p->kv_dtype != PA_DT_E4M3FN && p->kv_dtype != PA_DT_BF16) return PA_ERR_UNSUPPORTED;
   const bool bf16_kv = p->kv_dtype == PA_DT_BF16;
   const int kv_item = bf16_kv ? 2 : 1;  // bytes per cache element
@@ -157,7 +158,7 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   // kernel, which also covers other partition sizes for 16-token pages and up to 16 query rows.
   const bool tensor_path = !bf16_kv && p->partition_size == pa::tc::kItemTokens && p->tune_warps == 0;
   if (!tensor_path) {
-    if (p->block_size != 16 || eqG > 16) return PA_ERR_UNSUPPORTED;
+    if (p->block_size != 16 || eqG > 16 || q_item != 2) return PA_ERR_UNSUPPORTED;
     if (p->partition_size % (bf16_kv ? pa::kPageTokens : pa::kStageTokens) != 0 ||
         p->partition_size / p->block_size > 32)
       return PA_ERR_UNSUPPORTED;
@@ -168,7 +169,7 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   if (((p->k_stride_block * kv_item) & 15) || ((p->k_stride_head * kv_item) & 15) ||
       ((p->v_stride_block * kv_item) & 15) || ((p->v_stride_head * kv_item) & 15))
     return PA_ERR_ALIGNMENT;
-  if (p->q_stride_head != pa::kD || (p->q_stride_seq & 7)) return PA_ERR_ALIGNMENT;
+  if (p->q_stride_head != pa::kD || ((p->q_stride_seq * q_item) & 15)) return PA_ERR_ALIGNMENT;
   const bool per_token = p->kv_quant_mode == PA_QUANT_PER_TOKEN;
   if (per_token) {
     if (!aligned16(p->key_scale) || !aligned16(p->value_scale) || (p->kv_scale_stride_block & 3) ||
@@ -204,8 +205,9 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   k.pages_per_partition = p->partition_size / p->block_size;
   const int64_t cap = (int64_t)p->max_blocks_per_seq * p->block_size;
   k.ctx_cap = cap > 0x7fffffff ? 0x7fffffff : (int32_t)cap;
-  k.q_stride_seq = p->q_stride_seq * 2;    // bf16 -> bytes
-  k.q_stride_head = p->q_stride_head * 2;
+  k.q_stride_seq = p->q_stride_seq * q_item;    // elements -> bytes
+  k.q_stride_head = p->q_stride_head * q_item;
+  k.q_is_fp8 = q_item == 1;
   k.k_stride_block = p->k_stride_block * kv_item;   // elements -> bytes
   k.k_stride_head = p->k_stride_head * kv_item;
   k.v_stride_block = p->v_stride_block * kv_item;

@@ -42,6 +42,7 @@ struct KernelParams {
   int64_t tmp_stride_seq, tmp_stride_head, tmp_stride_part, tmp_stride_row;
 
   int32_t q_quant_mode, kv_quant_mode;
+  int32_t q_is_fp8;            // query rows are e4m3fn (1 byte per element) instead of bf16
   float softmax_scale;
 
   // shared-memory carve (byte offsets from the dynamic shared base) and ring geometry

@@ -555,10 +555,15 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         const int n = ps * 8 + n0;
         const int row = it.rb * QR + n;              // row inside the kv head's query group
         if (n < QR && row < p.eqG) {
-          const uint4* src = reinterpret_cast<const uint4*>(
-              p.q + (int64_t)it.seq * p.q_stride_seq + (int64_t)(it.head * p.eqG + row) * p.q_stride_head + qq * 64);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) raw[ps][e] = __ldg(src + e);
+          // this lane's 32 elements of the row: 64 bytes of bf16, or 32 bytes of e4m3
+          const uint8_t* row_ptr = p.q + (int64_t)it.seq * p.q_stride_seq + (int64_t)(it.head * p.eqG + row) * p.q_stride_head;
+          const uint4* src = reinterpret_cast<const uint4*>(row_ptr + (p.q_is_fp8 ? qq * 32 : qq * 64));
+          raw[ps][0] = __ldg(src);
+          raw[ps][1] = __ldg(src + 1);
+          if (!p.q_is_fp8) {
+            raw[ps][2] = __ldg(src + 2);
+            raw[ps][3] = __ldg(src + 3);
+          }
         }
       }
     };
@@ -640,6 +645,18 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         amax = quad_max(amax);
         float pre = 1.0f, inv_pre = 1.0f;
         const int be = (int)((__float_as_uint(amax) >> 23) & 0xff);
+        if (p.q_is_fp8) {
+          // e4m3 rows are the hi half as they are (the lo half is zero, no pre-scale)
+          if (n < QR) {
+            const int nl = QR + n;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              const uint32_t dst = qt + (2 * qq + c) * 128;
+              sts128(dst + (n >> 3) * 1024 + (n & 7) * 16, qv[c]);
+              sts128(dst + (nl >> 3) * 1024 + (nl & 7) * 16, make_uint4(0u, 0u, 0u, 0u));
+            }
+          }
+        } else {
         if (be > 30 && be < 225) {
           pre = __uint_as_float((uint32_t)(254 + 7 - be) << 23);
           inv_pre = __uint_as_float((uint32_t)(be - 7) << 23);
@@ -666,6 +683,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
             sts128(dst + (nl >> 3) * 1024 + (nl & 7) * 16, make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]));
           }
         }
+        }  // bf16 rows
         if (qq == 0 && n < QR) {
           float qs = 1.0f;
           if (p.q_quant_mode == PA_QUANT_PER_TENSOR) qs = __ldg(p.q_scale);
