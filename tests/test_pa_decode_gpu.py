@@ -267,3 +267,28 @@ def test_fp8_query_with_query_scale(heads, ql, bs, kvq, qmode):
     ref = pa_oracle.paged_attention(q_deq, inp.key_cache, inp.value_cache, inp.block_tables, inp.context_lens,
                                     inp.query_indptr(), ks, vs)
     assert_close(unpack_mtp(out, cfg.num_seqs, ql, hkv), ref, what=f"fp8 query {qmode}")
+
+
+@pytest.mark.parametrize("bs", [16, 64, 1024])
+@pytest.mark.parametrize("heads,ql,quant", [((8, 1), 1, "per_tensor"), ((16, 2), 2, "per_token")])
+def test_transposed_value_layout(bs, heads, ql, quant):
+    """Value cache in the reference's shuffled layout [NB, Hkv, bs/16, D, 16] (test_pa_mtp.py:472-497):
+    same results as the normal layout, ragged last pages included."""
+    from triton_op_b200 import paged_attention_decode
+    from triton_op_b200.inputs import DecodeConfig, make_inputs, shuffle_value_cache_layout, unpack_mtp
+    hq, hkv = heads
+    cfg = DecodeConfig("transv", 4, hq, hkv, bs, ql, ("fixed", 1), quant=quant)
+    inp = make_inputs(cfg, seed=23, device=DEV, context_lens=torch.tensor([1300, 257, 4097, 15]))
+    v_t = shuffle_value_cache_layout(inp.value_cache)
+    assert v_t.dim() == 5 and v_t.shape[2] == bs // 16 and v_t.shape[4] == 16
+    # garbage (NaN patterns) behind the end of every context must not leak through the other layout either
+    out = torch.full_like(inp.query, float("nan"))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    paged_attention_decode(out, inp.query, inp.key_cache, v_t, inp.context_lens, inp.block_tables,
+                           inp.softmax_scale, ql, inp.max_context, torch.bfloat16, None, inp.key_scale,
+                           inp.value_scale, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert_close(unpack_mtp(out, cfg.num_seqs, ql, hkv), oracle_output(inp), what=f"trans_v bs={bs}")
+    normal, _ = run_operator(inp)
+    assert torch.equal(unpack_mtp(out, cfg.num_seqs, ql, hkv), normal)     # same products, same order

@@ -151,7 +151,11 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   const int kv_item = bf16_kv ? 2 : 1;  // bytes per cache element
   if (bf16_kv && p->kv_quant_mode == PA_QUANT_PER_TOKEN) return PA_ERR_UNSUPPORTED;
   if (p->block_size != 16 && p->block_size != 64 && p->block_size != 1024) return PA_ERR_UNSUPPORTED;
-  if (p->v_layout != PA_V_NORMAL) return PA_ERR_UNSUPPORTED;
+  // Transposed values [NB, Hkv, bs/16, D, 16] (e4m3): a 16-token page is the same bytes as the
+  // normal layout; longer pages are served by the tcgen05 kernel as 2 KB runs.
+  const bool v_trans = p->v_layout == PA_V_TRANSPOSED && p->block_size != 16;
+  if (p->v_layout != PA_V_NORMAL && p->v_layout != PA_V_TRANSPOSED) return PA_ERR_UNSUPPORTED;
+  if (p->v_layout == PA_V_TRANSPOSED && p->kv_dtype != PA_DT_E4M3FN) return PA_ERR_UNSUPPORTED;
   if (p->alibi_slopes) return PA_ERR_UNSUPPORTED;
   if (eqG > 64) return PA_ERR_UNSUPPORTED;
   // tcgen05 kernel: 256-token partitions.  tune_warps == 4 / 8 explicitly asks for the mma.sync
@@ -239,7 +243,8 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   plan->tensor_path = tensor_path;
   memset(&plan->vmap, 0, sizeof(plan->vmap));
   if (plan->tensor_path) {
-    if (p->block_size >= 64) {
+    k.v_trans = v_trans ? 1 : 0;
+    if (p->block_size >= 64 && !v_trans) {
       rc = encode_value_map(p, &plan->vmap);
       if (rc != PA_OK) return rc;
     }

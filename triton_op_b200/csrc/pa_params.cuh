@@ -43,6 +43,7 @@ struct KernelParams {
 
   int32_t q_quant_mode, kv_quant_mode;
   int32_t q_is_fp8;            // query rows are e4m3fn (1 byte per element) instead of bf16
+  int32_t v_trans;             // value cache is [NB, Hkv, bs/16, D, 16]: every 16 tokens a [D][16] run of 2 KB
   float softmax_scale;
 
   // shared-memory carve (byte offsets from the dynamic shared base) and ring geometry

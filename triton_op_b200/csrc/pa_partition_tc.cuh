@@ -472,9 +472,11 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     const uint32_t ring = is_v ? v_ring : k_ring;
     const uint64_t pol = l2_policy_evict_first();
     // which page of the item this lane copies from
+    // (transposed value layout: lane = one of the item's sixteen 16-token runs)
+    const bool vt = BS != 16 && is_v && p.v_trans != 0;
     auto my_page = [&]() -> int {
       if (BS == 16) return lane;
-      if (BS == 64) return is_v ? lane : (lane >> 3);
+      if (BS == 64) return is_v ? (vt ? (lane >> 2) : lane) : (lane >> 3);
       return 0;
     };
     auto load_page_id = [&](const TcItem& it) -> int {
@@ -519,6 +521,12 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (lane == 0) mbar_arrive_expect_tx(full, npg * kPageBytes);
         __syncwarp();
         if (lane < npg) bulk_g2s(dst + lane * kPageBytes, src, kPageBytes, full, pol);
+      } else if (vt) {       // transposed values: 2 KB runs [128 d][16 tok], laid out in the slot as 16-token pages
+        const int runs = (it.ntok + 15) >> 4;
+        const int first_run = BS == 64 ? (lane & 3) : ((it.tok0 % BS) >> 4) + lane;   // run inside the page
+        if (lane == 0) mbar_arrive_expect_tx(full, runs * kPageBytes);
+        __syncwarp();
+        if (lane < runs) bulk_g2s(dst + lane * kPageBytes, src + (int64_t)first_run * kPageBytes, kPageBytes, full, pol);
       } else if (BS == 64) {
         if (lane == 0) mbar_arrive_expect_tx(full, npg * 8192);
         __syncwarp();
@@ -742,13 +750,14 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (!wait(bar(kBarPFull, g), gu & 1) || !wait(bar(kBarVFull, vslot), vuse & 1)) { fail(); break; }
         stamp(3, j, 2);
         fence_after_sync();
-        const uint64_t vd = BS == 16 ? smem_desc(v_ring + vslot * kHalfSlot, 2048, 128)
-                                     : smem_desc_swizzled(v_ring + vslot * kHalfSlot, G::kVSpan);
+        const bool v16 = BS == 16 || p.v_trans != 0;   // the slot holds [128 d][16 tok] runs
+        const uint64_t vd = v16 ? smem_desc(v_ring + vslot * kHalfSlot, 2048, 128)
+                                : smem_desc_swizzled(v_ring + vslot * kHalfSlot, G::kVSpan);
         const uint64_t pd = smem_desc(p_tiles + g * kPTile, kPLbo, kPSbo);
         const uint32_t d0 = tmem_base + g * 4 * N + 2 * N + (int)(gu & 1) * N;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t ad = vd + (uint64_t)(G::v_kstep(ks) >> 4);
+          const uint64_t ad = vd + (uint64_t)((v16 ? Geo<16>::v_kstep(ks) : G::v_kstep(ks)) >> 4);
           const uint64_t bd = pd + (uint64_t)((ks * kPStep) >> 4);
           if (leader) mma_f8_ss(d0, ad, bd, kIdesc, ks > 0);
         }
@@ -1004,12 +1013,14 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         }
         if (!wait(bar(kBarVFull, vslot), (uint32_t)(i / NSV) & 1)) return false;
         const uint32_t vrow = v_ring + vslot * kHalfSlot;                  // this lane clears row = head dim r
+        const bool v16 = BS == 16 || p.v_trans != 0;  // the slot holds [128 d][16 tok] runs
+        auto v_at = [&](int g16) -> int { return v16 ? Geo<16>::v_chunk(r, g16) : G::v_chunk(r, g16); };
         const int first_bad = it.ntok >> 4;           // 16-token group holding the first invalid token
         const int keep = it.ntok & 15;                // valid tokens in that group
         for (int g16 = first_bad; g16 < 16; ++g16) {
           uint4 val = make_uint4(0u, 0u, 0u, 0u);
           if (g16 == first_bad && keep > 0) {
-            val = lds128(vrow + G::v_chunk(r, g16));
+            val = lds128(vrow + v_at(g16));
             uint32_t w[4] = {val.x, val.y, val.z, val.w};
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
@@ -1018,7 +1029,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
             }
             val = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          sts128(vrow + G::v_chunk(r, g16), val);
+          sts128(vrow + v_at(g16), val);
         }
       }
       fence_proxy_async();   // P^T and the cleared V bytes are read by the tensor core

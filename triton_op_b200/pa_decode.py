@@ -245,6 +245,9 @@ def _build_params(output, query, key_cache, value_cache, sequence_lengths, block
     if v_layout == _lib.PA_V_NORMAL:
         if not (tuple(value_cache.shape) == (num_blocks, num_kv_heads, head_size, kv_block_size)):
             _fail("value_cache must be [num_blocks, num_kv_heads, head_size, block_size]")
+    else:   # transposed: [num_blocks, num_kv_heads, block_size/x, head_size, x] (test_pa_mtp.py:472-497)
+        if not (tuple(value_cache.shape) == (num_blocks, num_kv_heads, kv_block_size // x, head_size, x)):
+            _fail(f"transposed value_cache must be [num_blocks, num_kv_heads, block_size/{x}, head_size, {x}]")
     if not (block_tables.dim() == 2 and block_tables.shape[0] == num_seqs and sequence_lengths.numel() == num_seqs):
         _fail("block_tables must be [num_seqs, max_blocks] and sequence_lengths [num_seqs]")
     if not (partition_size > 0 and (partition_size % kv_block_size == 0 or kv_block_size % partition_size == 0)):
