@@ -176,6 +176,48 @@ int64_t pa_packed_triple_floats(int32_t num_rows, int32_t head_size);
 int pa_merge_packed_triples_sm100(void* out, int64_t out_stride_row, const float* packed,
                                   int32_t num_shards, int32_t num_rows, int32_t head_size, void* stream);
 
+/*
+ * KV-cache write side (the step before the decode path; the reference builds its caches offline
+ * with torch permutes, test_pa_mtp.py:109-172, and quantises them per token with
+ * quantize_kv_cache_symmetric, :294-369): quantise T new key / value tokens and scatter them
+ * into the paged layouts above.  Token t goes to slot slots[t] = block * block_size + offset;
+ * negative slots are skipped.
+ *   kv_quant_mode PA_QUANT_NONE       bf16 caches, bits copied
+ *                 PA_QUANT_PER_TENSOR e4m3fn caches, q = x / *key_scale (read)
+ *                 PA_QUANT_PER_TOKEN  e4m3fn caches, scale = max(amax(vector)/448, 1e-12) is WRITTEN to
+ *                                     key_scale / value_scale [NB, Hkv, bs, 1], q = x / scale
+ * Division is IEEE, conversion round-to-nearest-even, so in-range bytes equal torch's
+ * (x.float() / scale).to(torch.float8_e4m3fn); values beyond +-448 (possible with a static
+ * per-tensor scale) saturate, where torch's cast would store NaN.
+ */
+typedef struct PaCacheWriteParams {
+  uint32_t struct_size;        /* = sizeof(PaCacheWriteParams) */
+  uint32_t abi_version;        /* = PA_ABI_VERSION */
+  const void* key;             /* [T, Hkv, D] bf16, last dim contiguous */
+  const void* value;           /* [T, Hkv, D] bf16 */
+  const int64_t* slot_mapping; /* [T] */
+  void* key_cache;             /* [NB, Hkv, D/x, bs, x] */
+  void* value_cache;           /* [NB, Hkv, D, bs] or transposed [NB, Hkv, bs/16, D, 16] */
+  float* key_scale;            /* see kv_quant_mode */
+  float* value_scale;
+  int32_t* status;             /* optional; PA_DEV_BAD_PAGE_ID when a slot lies outside the pool */
+  int32_t num_tokens;          /* T */
+  int32_t num_kv_heads;
+  int32_t head_size;           /* 128 */
+  int32_t block_size;
+  int32_t num_blocks;
+  int32_t kv_dtype;            /* PaDType */
+  int32_t kv_quant_mode;       /* PaQuantMode */
+  int32_t v_layout;            /* PaVLayout */
+  int64_t key_stride_token, key_stride_head;       /* elements */
+  int64_t value_stride_token, value_stride_head;
+  int64_t k_stride_block, k_stride_head;           /* caches, elements */
+  int64_t v_stride_block, v_stride_head;
+  int64_t kv_scale_stride_block, kv_scale_stride_head;
+} PaCacheWriteParams;
+
+int pa_cache_write_sm100(const PaCacheWriteParams* params, void* stream);
+
 /* Bytes of dynamic shared memory and the grid the partition kernel would use for `params`
  * (host-only query, launches nothing).  Any output pointer may be NULL. */
 int pa_query_launch_sm100(const PaDecodeParams* params, int32_t* grid_ctas, int32_t* cta_threads,

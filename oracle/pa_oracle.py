@@ -218,3 +218,46 @@ def compare_arrays(arr1: np.ndarray, arr2: np.ndarray, k: int = 5,
         "threshold_stats": stats,
         "nan_info": {"arr1_nan_count": int(np.isnan(a).sum()), "arr2_nan_count": int(np.isnan(b).sum())},
     }
+
+
+def write_kv_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                   slot_mapping: torch.Tensor, key_scale: Optional[torch.Tensor] = None,
+                   value_scale: Optional[torch.Tensor] = None) -> None:
+    """CPU statement of the cache write side, in place on the cache (and per-token scale) tensors.
+
+    Layouts as the reference builds them: keys ``[NB, Hkv, D/x, bs, x]`` (test_pa_mtp.py:150-151),
+    values ``[NB, Hkv, D, bs]`` (:162) or shuffled ``[NB, Hkv, bs/x, D, x]`` (:472-497).  Per-token
+    quantisation follows quantize_kv_cache_symmetric (:294-369) with the build's quantiser
+    ``scale = max(amax / 448, 1e-12)``, ``q = (x / scale) -> e4m3fn``; 0-dim scales are read.
+    ``key`` / ``value`` ``[T, Hkv, D]``; ``slot_mapping [T]`` (block * bs + offset, negative = skip).
+    """
+    T, hkv, d = key.shape
+    nb, bs = key_cache.shape[0], key_cache.shape[3]
+    x = key_cache.shape[4]
+    fp8 = key_cache.dtype != torch.bfloat16
+    trans = value_cache.dim() == 5
+    for t in range(T):
+        slot = int(slot_mapping[t])
+        if slot < 0:
+            continue
+        blk, off = slot // bs, slot % bs
+        for which, src, cache, scale in (("k", key, key_cache, key_scale), ("v", value, value_cache, value_scale)):
+            vec = src[t].float()                                  # [Hkv, D]
+            if fp8:
+                # values beyond the e4m3fn range saturate to +-448 (a plain torch cast would store NaN)
+                if scale is None:
+                    q = vec.clamp(-448.0, 448.0).to(cache.dtype)
+                elif scale.dim() == 0:
+                    q = (vec / scale.float()).clamp(-448.0, 448.0).to(cache.dtype)
+                else:
+                    s = (vec.abs().amax(dim=-1, keepdim=True) / 448.0).clamp_min(1e-12)    # [Hkv, 1]
+                    scale[blk, :, off, 0] = s[:, 0]
+                    q = (vec / s).to(cache.dtype)
+            else:
+                q = src[t]
+            if which == "k":
+                cache[blk, :, :, off, :] = q.view(hkv, d // x, x)
+            elif trans:
+                cache[blk, :, off // x, :, off % x] = q
+            else:
+                cache[blk, :, :, off] = q

@@ -22,7 +22,7 @@ PA_NOALLOC_SCRATCH_BYTES = 16 << 20
 
 EXPORTS = (
     "pa_decode_sm100", "pa_decode_noalloc_sm100", "pa_partition_sm100", "pa_reduce_sm100", "pa_merge_triples_sm100",
-    "pa_merge_packed_triples_sm100", "pa_packed_triple_floats", "pa_query_launch_sm100", "pa_strerror", "pa_last_cuda_error", "pa_abi_version",
+    "pa_merge_packed_triples_sm100", "pa_packed_triple_floats", "pa_cache_write_sm100", "pa_query_launch_sm100", "pa_strerror", "pa_last_cuda_error", "pa_abi_version",
 )
 
 
@@ -47,6 +47,20 @@ class PaDecodeParams(C.Structure):
             "q_dtype", "kv_dtype", "out_dtype", "q_quant_mode", "kv_quant_mode", "v_layout")]
         + [("softmax_scale", C.c_float)]
         + [(n, C.c_int32) for n in ("tune_warps", "tune_stages", "tune_ctas", "tune_vstages")]
+    )
+
+
+class PaCacheWriteParams(C.Structure):
+    """Field-for-field mirror of ``struct PaCacheWriteParams``."""
+    _fields_ = (
+        [("struct_size", C.c_uint32), ("abi_version", C.c_uint32)]
+        + [(n, C.c_void_p) for n in ("key", "value", "slot_mapping", "key_cache", "value_cache",
+                                     "key_scale", "value_scale", "status")]
+        + [(n, C.c_int32) for n in ("num_tokens", "num_kv_heads", "head_size", "block_size", "num_blocks",
+                                    "kv_dtype", "kv_quant_mode", "v_layout")]
+        + [(n, C.c_int64) for n in ("key_stride_token", "key_stride_head", "value_stride_token", "value_stride_head",
+                                    "k_stride_block", "k_stride_head", "v_stride_block", "v_stride_head",
+                                    "kv_scale_stride_block", "kv_scale_stride_head")]
     )
 
 
@@ -87,6 +101,8 @@ def lib() -> C.CDLL:
     L.pa_packed_triple_floats.argtypes = [C.c_int32, C.c_int32]
     L.pa_packed_triple_floats.restype = C.c_int64
     L.pa_query_launch_sm100.argtypes = [P] + [C.POINTER(C.c_int32)] * 4
+    L.pa_cache_write_sm100.argtypes = [C.POINTER(PaCacheWriteParams), C.c_void_p]
+    L.pa_cache_write_sm100.restype = C.c_int
     for name in ("pa_decode_sm100", "pa_decode_noalloc_sm100", "pa_partition_sm100", "pa_reduce_sm100",
                  "pa_merge_triples_sm100", "pa_query_launch_sm100", "pa_last_cuda_error",
                  "pa_abi_version"):

@@ -13,6 +13,7 @@
 #include "pa_partition_fp8.cuh"
 #include "pa_partition_tc.cuh"
 #include "pa_reduce.cuh"
+#include "pa_cache_write.cuh"
 
 namespace {
 
@@ -572,6 +573,60 @@ int pa_merge_packed_triples_sm100(void* out, int64_t out_stride_row, const float
   const int64_t o_off = stride - (int64_t)num_rows * head_size;
   return launch_merge(out, out_stride_row, packed, packed + num_rows, packed + o_off, num_shards, num_rows,
                       head_size, stride, stride, stream);
+}
+
+int pa_cache_write_sm100(const PaCacheWriteParams* p, void* stream) {
+  if (!p) return PA_ERR_NULL_POINTER;
+  if (p->struct_size != sizeof(PaCacheWriteParams) || p->abi_version != PA_ABI_VERSION) return PA_ERR_ABI;
+  if (p->num_tokens < 0 || p->num_kv_heads <= 0 || p->block_size <= 0 || p->num_blocks <= 0) return PA_ERR_BAD_SHAPE;
+  if (p->head_size != pa::kD) return PA_ERR_UNSUPPORTED;
+  if (!p->key || !p->value || !p->slot_mapping || !p->key_cache || !p->value_cache) return PA_ERR_NULL_POINTER;
+  const bool fp8 = p->kv_dtype == PA_DT_E4M3FN;
+  if (!fp8 && p->kv_dtype != PA_DT_BF16) return PA_ERR_UNSUPPORTED;
+  if (fp8 && p->kv_quant_mode != PA_QUANT_NONE && (!p->key_scale || !p->value_scale)) return PA_ERR_NULL_POINTER;
+  if (!fp8 && p->kv_quant_mode != PA_QUANT_NONE) return PA_ERR_UNSUPPORTED;
+  const bool v_trans = p->v_layout == PA_V_TRANSPOSED;
+  if (v_trans && (!fp8 || p->block_size % 16 != 0)) return PA_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(p->key) & 7u) || (reinterpret_cast<uintptr_t>(p->value) & 7u) ||
+      (p->key_stride_token & 3) || (p->key_stride_head & 3) || (p->value_stride_token & 3) ||
+      (p->value_stride_head & 3) || !aligned16(p->key_cache) || ((p->k_stride_block * (fp8 ? 1 : 2)) & 15) ||
+      ((p->k_stride_head * (fp8 ? 1 : 2)) & 15))
+    return PA_ERR_ALIGNMENT;
+  if (p->num_tokens == 0) return PA_OK;
+  pa::CacheWriteParams k;
+  memset(&k, 0, sizeof(k));
+  k.key = static_cast<const uint8_t*>(p->key);
+  k.value = static_cast<const uint8_t*>(p->value);
+  k.slots = p->slot_mapping;
+  k.key_cache = static_cast<uint8_t*>(p->key_cache);
+  k.value_cache = static_cast<uint8_t*>(p->value_cache);
+  k.k_scale = p->key_scale;
+  k.v_scale = p->value_scale;
+  k.T = p->num_tokens;
+  k.Hkv = p->num_kv_heads;
+  k.block_size = p->block_size;
+  k.num_blocks = p->num_blocks;
+  k.kv_is_fp8 = fp8;
+  k.quant_mode = p->kv_quant_mode;
+  k.v_trans = v_trans;
+  k.key_stride_tok = p->key_stride_token;
+  k.key_stride_head = p->key_stride_head;
+  k.value_stride_tok = p->value_stride_token;
+  k.value_stride_head = p->value_stride_head;
+  k.kc_stride_block = p->k_stride_block;
+  k.kc_stride_head = p->k_stride_head;
+  k.vc_stride_block = p->v_stride_block;
+  k.vc_stride_head = p->v_stride_head;
+  k.ks_stride_block = p->kv_scale_stride_block;
+  k.ks_stride_head = p->kv_scale_stride_head;
+  k.status = p->status;
+  const int64_t pairs = (int64_t)p->num_tokens * p->num_kv_heads;
+  const int64_t blocks = (pairs + 3) / 4;
+  if (blocks > 0x7fffffff) return PA_ERR_TOO_LARGE;
+  pa::pa_cache_write_kernel<<<(unsigned)blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(k);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return PA_OK;
 }
 
 int pa_query_launch_sm100(const PaDecodeParams* params, int32_t* grid_ctas, int32_t* cta_threads,
