@@ -33,7 +33,7 @@ import torch
 
 def masked_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                      softmax_scale: float, output_dtype: torch.dtype,
-                     is_causal: bool = True) -> torch.Tensor:
+                     is_causal: bool = True, alibi_slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of ``query [q, Hq, D]`` over ``key/value [k, Hkv, D]`` (test_pa_mtp.py:175-220).
 
     KV heads are repeated to the query heads, scores are fp32, the causal rule lets query row i
@@ -43,6 +43,14 @@ def masked_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor
     key = key.repeat_interleave(hq // hkv, dim=1)
     value = value.repeat_interleave(hq // hkv, dim=1)
     scores = torch.einsum("qhd,khd->hqk", query.float(), key.float()) * softmax_scale
+    if alibi_slopes is not None:
+        # the kernels' bias, pa_decode_triton_gluon_fp8.py:905-908: slope[head] * (key position - (context - 1)),
+        # added to the scaled scores.  (The reference's PyTorch path has no ALiBi and its tests never pass
+        # slopes; the Gluon kernel loads slopes for the first G rows of a kv head only, which leaves the later
+        # MTP tokens without bias -- here every row of a head gets its head's slope.)
+        kl = key.shape[0]
+        rel = torch.arange(kl, dtype=torch.float32, device=query.device) - (kl - 1)
+        scores = scores + alibi_slopes.float().view(-1, 1, 1) * rel.view(1, 1, -1)
     if is_causal:
         ql, kl = query.shape[0], key.shape[0]
         bias = torch.zeros(ql, kl, dtype=query.dtype, device=query.device)
@@ -86,7 +94,8 @@ def paged_attention(query: torch.Tensor, key_cache: torch.Tensor, value_cache: t
                     block_tables: torch.Tensor, context_lens: torch.Tensor,
                     query_indptr: torch.Tensor,
                     key_scale: Optional[torch.Tensor] = None,
-                    value_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    value_scale: Optional[torch.Tensor] = None,
+                    alibi_slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The reference's paged multi-head attention (test_pa_mtp.py:223-291).
 
     query ``[total_q, Hq, D]`` split per sequence by ``query_indptr [S+1]``; caches in the paged
@@ -102,7 +111,8 @@ def paged_attention(query: torch.Tensor, key_cache: torch.Tensor, value_cache: t
     for s in range(query_indptr.shape[0] - 1):
         ctx = int(context_lens[s].item())
         keys, values = gather_sequence(k_flat, v_flat, block_tables[s], ctx, bs, key_scale, value_scale)
-        outs.append(masked_attention(q_split[s], keys, values, softmax_scale, out_dtype, is_causal=True))
+        outs.append(masked_attention(q_split[s], keys, values, softmax_scale, out_dtype, is_causal=True,
+                                     alibi_slopes=alibi_slopes))
     return torch.cat(outs)
 
 

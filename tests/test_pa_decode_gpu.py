@@ -292,3 +292,31 @@ def test_transposed_value_layout(bs, heads, ql, quant):
     assert_close(unpack_mtp(out, cfg.num_seqs, ql, hkv), oracle_output(inp), what=f"trans_v bs={bs}")
     normal, _ = run_operator(inp)
     assert torch.equal(unpack_mtp(out, cfg.num_seqs, ql, hkv), normal)     # same products, same order
+
+
+@pytest.mark.parametrize("heads,ql,bs,quant", [((32, 8), 1, 16, "per_tensor"), ((8, 1), 1, 64, "per_token"),
+                                               ((16, 2), 2, 1024, "per_token"), ((16, 1), 1, 16, "per_tensor"),
+                                               ((10, 1), 4, 16, "per_tensor")])
+def test_alibi_slopes(heads, ql, bs, quant):
+    """ALiBi bias slope[head] * (key position - (context - 1)) (pa_decode_triton_gluon_fp8.py:905-908);
+    the reference never tests it, so the oracle's statement of that formula is the yardstick."""
+    from oracle import pa_oracle
+    from triton_op_b200 import paged_attention_decode
+    from triton_op_b200.inputs import DecodeConfig, make_inputs, unpack_mtp
+    hq, hkv = heads
+    cfg = DecodeConfig("alibi", 3, hq, hkv, bs, ql, ("fixed", 1), quant=quant)
+    inp = make_inputs(cfg, seed=29, device=DEV, context_lens=torch.tensor([900, 2050, 17]))
+    slopes = (2.0 ** (-8.0 * torch.arange(1, hq + 1, dtype=torch.float32) / hq)).to(DEV)   # the usual geometric slopes
+    out = torch.full_like(inp.query, float("nan"))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    res = paged_attention_decode(out, inp.query, inp.key_cache, inp.value_cache, inp.context_lens, inp.block_tables,
+                                 inp.softmax_scale, ql, inp.max_context, torch.bfloat16, None, inp.key_scale,
+                                 inp.value_scale, 0, slopes, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ks, vs = inp.flat_scales()
+    ref = pa_oracle.paged_attention(inp.query_tokens, inp.key_cache, inp.value_cache, inp.block_tables, inp.context_lens,
+                                    inp.query_indptr(), ks, vs, alibi_slopes=slopes)
+    assert_close(unpack_mtp(out, cfg.num_seqs, ql, hkv), ref, what="alibi")
+    no_bias, _ = run_operator(inp)
+    assert (unpack_mtp(out, cfg.num_seqs, ql, hkv).float() - no_bias.float()).abs().max() > 1e-2   # the bias matters

@@ -157,13 +157,13 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   const bool v_trans = p->v_layout == PA_V_TRANSPOSED && p->block_size != 16;
   if (p->v_layout != PA_V_NORMAL && p->v_layout != PA_V_TRANSPOSED) return PA_ERR_UNSUPPORTED;
   if (p->v_layout == PA_V_TRANSPOSED && p->kv_dtype != PA_DT_E4M3FN) return PA_ERR_UNSUPPORTED;
-  if (p->alibi_slopes) return PA_ERR_UNSUPPORTED;
+  // (ALiBi: tcgen05 kernel only, checked below)
   if (eqG > 64) return PA_ERR_UNSUPPORTED;
   // tcgen05 kernel: 256-token partitions.  tune_warps == 4 / 8 explicitly asks for the mma.sync
   // kernel, which also covers other partition sizes for 16-token pages and up to 16 query rows.
   const bool tensor_path = !bf16_kv && p->partition_size == pa::tc::kItemTokens && p->tune_warps == 0;
   if (!tensor_path) {
-    if (p->block_size != 16 || eqG > 16 || q_item != 2) return PA_ERR_UNSUPPORTED;
+    if (p->block_size != 16 || eqG > 16 || q_item != 2 || p->alibi_slopes) return PA_ERR_UNSUPPORTED;
     if (p->partition_size % (bf16_kv ? pa::kPageTokens : pa::kStageTokens) != 0 ||
         p->partition_size / p->block_size > 32)
       return PA_ERR_UNSUPPORTED;
@@ -192,6 +192,7 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   k.q_scale = p->query_scale;
   k.k_scale = p->key_scale;
   k.v_scale = p->value_scale;
+  k.alibi = p->alibi_slopes;
   k.exp_sums = p->exp_sums;
   k.max_logits = p->max_logits;
   k.tmp_out = static_cast<uint8_t*>(p->tmp_out);
@@ -335,9 +336,9 @@ int launch_partition_t(const LaunchPlan& plan, cudaStream_t stream) {
   return PA_OK;
 }
 
-template <int BS, int QR, bool PT, bool TRACE>
+template <int BS, int QR, bool PT, bool TRACE, bool ALIBI = false>
 int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
-  auto kern = pa::tc::pa_partition_fp8_tc_kernel<BS, QR, PT, TRACE>;
+  auto kern = pa::tc::pa_partition_fp8_tc_kernel<BS, QR, PT, TRACE, ALIBI>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
   if (e != cudaSuccess) return cuda_fail(e);
   kern<<<plan.grid, pa::tc::kThreads, plan.smem, stream>>>(plan.kp, plan.vmap);
@@ -349,6 +350,14 @@ int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
 template <int BS, bool TRACE>
 int launch_tensor_bs(const LaunchPlan& plan, cudaStream_t stream) {
   const bool pt = plan.per_token;
+  if (!TRACE && plan.kp.alibi != nullptr) {   // the ALiBi instantiations
+    switch (plan.rows) {
+      case 4: return pt ? launch_tensor_t<BS, 4, true, false, true>(plan, stream) : launch_tensor_t<BS, 4, false, false, true>(plan, stream);
+      case 8: return pt ? launch_tensor_t<BS, 8, true, false, true>(plan, stream) : launch_tensor_t<BS, 8, false, false, true>(plan, stream);
+      case 16: return pt ? launch_tensor_t<BS, 16, true, false, true>(plan, stream) : launch_tensor_t<BS, 16, false, false, true>(plan, stream);
+      default: return PA_ERR_UNSUPPORTED;
+    }
+  }
   switch (plan.rows) {
     case 4: return pt ? launch_tensor_t<BS, 4, true, TRACE>(plan, stream) : launch_tensor_t<BS, 4, false, TRACE>(plan, stream);
     case 8: return pt ? launch_tensor_t<BS, 8, true, TRACE>(plan, stream) : launch_tensor_t<BS, 8, false, TRACE>(plan, stream);

@@ -18,6 +18,7 @@ struct KernelParams {
   const float* q_scale;
   const float* k_scale;
   const float* v_scale;
+  const float* alibi;          // [Hkv * G] slopes or null
   float* exp_sums;
   float* max_logits;
   uint8_t* tmp_out;            // bf16

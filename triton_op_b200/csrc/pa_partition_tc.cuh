@@ -77,8 +77,9 @@ __host__ __device__ constexpr int q_tile_bytes(int qr) { return mma_n(qr) * kD; 
 // with the same query rows share a tile, so the two parts are used as two rings with their own
 // counters.
 constexpr int kQHdr = 64;    // offset of the item header behind the tile
+constexpr int kQSlope = 80;  // offset of the tile's 16 ALiBi slopes (base-2 logit domain) behind the tile
 __host__ __device__ constexpr int q_slot_bytes(int qr, bool /*per_token*/) {
-  return q_tile_bytes(qr) + kQHdr + 16;
+  return q_tile_bytes(qr) + kQSlope + 64;
 }
 // P^T tile of one item: 8 k-steps x [row blocks of 8][2 K units][8 rows][16 tokens].  The strides
 // are padded off the 128-byte grid (k-step stride = 48 mod 128) so that byte stores of one warp
@@ -359,7 +360,9 @@ struct Geo {
 // BS: tokens per page.  QR: query rows per work item (4, 8 or 16; the host picks the smallest
 // that holds eqG, or 16 with several row blocks).  PER_TOKEN: per-token-per-head K/V scales.
 // TRACE: compile the clock stamps in (tuning builds).
-template <int BS, int QR, bool PER_TOKEN, bool TRACE>
+// ALIBI: add slope[head] * (key position - (context - 1)) to the logits
+// (pa_decode_triton_gluon_fp8.py:905-908).
+template <int BS, int QR, bool PER_TOKEN, bool TRACE, bool ALIBI = false>
 __global__ void __launch_bounds__(kThreads, 1)
 pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap vmap) {
   using G = Geo<BS>;
@@ -698,6 +701,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           if (p.q_quant_mode == PA_QUANT_PER_TOKEN && row < p.eqG)
             qs = __ldg(p.q_scale + (int64_t)it.seq * p.q_scale_stride_seq + it.head * p.eqG + row);
           sts32(aux + n * 4, __float_as_uint(inv_pre * qs));
+          if (ALIBI)   // slope of the row's query head, in the base-2 logit domain
+            sts32(aux + kQSlope + n * 4, __float_as_uint(row < p.eqG ? __ldg(p.alibi + it.head * p.G + row % p.G) * kLog2e : 0.f));
         }
       }
       fence_proxy_async();  // the tile is read by the tensor core (async proxy)
@@ -852,6 +857,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       // are rolled): the positive factor that turns a raw product into a base-2 logit, and the
       // causal limit.  The query slot is released when pass 2 has read them for the last time.
       float row_scale[RC];
+      float slope[RC];   // ALiBi only
       int lim[RC];  // row q sees token j iff (tokens from j to the end of the context) > lim[q]
       auto load_row_consts = [&](int ch) {
 #pragma unroll
@@ -864,6 +870,11 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
             // > 0 always, so that a masked -inf stays -inf and maxima commute with the factor
             row_scale[q4 + e] = fmaxf(__uint_as_float(w[e]) * base_scale, 1e-30f);
             lim[q4 + e] = (int)li[e];
+          }
+          if (ALIBI) {
+            const uint4 c = lds128(aux + kQSlope + (ch * RC + q4) * 4);
+            slope[q4] = __uint_as_float(c.x), slope[q4 + 1] = __uint_as_float(c.y);
+            slope[q4 + 2] = __uint_as_float(c.z), slope[q4 + 3] = __uint_as_float(c.w);
           }
         }
       };
@@ -881,9 +892,13 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (room[0] <= 0) vs_tok[0] = 0.f;
         if (room[1] <= 0) vs_tok[1] = 0.f;
       }
+      // key position relative to the last one, for ALiBi: -(room - 1)
+      const float rel_pos[2] = {(float)(1 - room[0]), (float)(1 - room[1])};
       // Raw logits of one chunk of rows for this lane's two tokens: the product (times the
       // token's key scale), -inf where the row does not see the token.  The row's factor is
-      // applied later, fused into the exponent's argument.
+      // applied later, fused into the exponent's argument.  (With ALiBi the bias differs per
+      // token, so the factor and the bias are applied here and the maxima are those of the
+      // finished logits.)
       auto raw_logits = [&](int ch, float (&s)[2][RC]) {
         uint32_t h[2][8], l[2][8];
         load_rows(tmem_grp, ch, h[0], l[0]);
@@ -896,6 +911,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           for (int q = 0; q < RC; ++q) {
             float v = row_value(h[tg], l[tg], q);
             if (PER_TOKEN) v *= ks_tok[tg];
+            if (ALIBI) v = fmaf(v, row_scale[q], slope[q] * rel_pos[tg]);
             s[tg][q] = room[tg] > lim[q] ? v : -INFINITY;
           }
         }
@@ -961,9 +977,16 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           const float4 m4 = *reinterpret_cast<const float4*>(rm + (ch * RC + q) * 4);
           const float m = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w));
           // exponent argument raw * factor - m * factor + 8 as one multiply-add per element
-          const float off = (m == -INFINITY) ? 8.0f : fmaf(-m, row_scale[q], 8.0f);
-          const float p0 = ex2(fmaf(s_keep[0][q], row_scale[q], off));
-          const float p1 = ex2(fmaf(s_keep[1][q], row_scale[q], off));
+          float p0, p1;
+          if (ALIBI) {   // s_keep holds finished logits
+            const float off = (m == -INFINITY) ? 8.0f : 8.0f - m;
+            p0 = ex2(s_keep[0][q] + off);
+            p1 = ex2(s_keep[1][q] + off);
+          } else {
+            const float off = (m == -INFINITY) ? 8.0f : fmaf(-m, row_scale[q], 8.0f);
+            p0 = ex2(fmaf(s_keep[0][q], row_scale[q], off));
+            p1 = ex2(fmaf(s_keep[1][q], row_scale[q], off));
+          }
           psum[q] = p0 + p1;
           split_hi_lo(PER_TOKEN ? p0 * vs_tok[0] : p0, hi[0][q], lo[0][q]);
           split_hi_lo(PER_TOKEN ? p1 * vs_tok[1] : p1, hi[1][q], lo[1][q]);
@@ -992,7 +1015,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         const float4 m4 = *reinterpret_cast<const float4*>(rm + r * 4);
         const float m = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w));
         const float sc = fmaxf(__uint_as_float(lds32(aux + r * 4)) * base_scale, 1e-30f);
-        m_fin[par * 16 + r] = (m == -INFINITY) ? m : m * sc;
+        m_fin[par * 16 + r] = (m == -INFINITY || ALIBI) ? m : m * sc;
       }
       __syncwarp();   // the query slot's scales were read until here
       if (lane == 0) mbar_arrive(bar(kBarQEmpty, slot));

@@ -319,6 +319,10 @@ def _build_params(output, query, key_cache, value_cache, sequence_lengths, block
     p.query_scale = q_scale_t.data_ptr() if q_scale_t is not None else None
     p.key_scale = k_scale_t.data_ptr() if k_scale_t is not None else None
     p.value_scale = v_scale_t.data_ptr() if v_scale_t is not None else None
+    if alibi_slopes is not None:
+        if not (isinstance(alibi_slopes, torch.Tensor) and alibi_slopes.dtype == torch.float32 and alibi_slopes.device == dev
+                and alibi_slopes.numel() == num_kv_heads * group and alibi_slopes.is_contiguous()):
+            _fail("alibi_slopes must be a contiguous fp32 tensor with one slope per query head on the output's device")
     p.alibi_slopes = alibi_slopes.data_ptr() if alibi_slopes is not None else None
     p.exp_sums, p.max_logits, p.tmp_out = exp_sums.data_ptr(), max_logits.data_ptr(), tmp_output.data_ptr()
     p.status = status.data_ptr() if status is not None else None
