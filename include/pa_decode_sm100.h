@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define PA_ABI_VERSION 1
+#define PA_ABI_VERSION 2
 
 typedef enum PaStatus {
   PA_OK = 0,
@@ -89,6 +89,9 @@ typedef struct PaDecodeParams {
   const float* key_scale;      /* per-tensor [1] / per-token [NB, Hkv, bs]; NULL when PA_QUANT_NONE */
   const float* value_scale;    /* same shape as key_scale */
   const float* alibi_slopes;   /* [Hkv*G] or NULL */
+  const float* sink_tokens;    /* [Hkv*G] or NULL: one sink logit per query head; the reduce adds
+                                * exp(sink - M) to a row's sum of weights (the reference's unused Gluon
+                                * reduce, pa_decode_triton_gluon_fp8.py:1117-1123).  Not applied to triples. */
 
   /* workspaces, caller-owned (reference: torch.zeros at pa_decode_triton_gluon_fp8.py:1729-1733).
    * They need not be zeroed: every partition the reduce reads is written by the partition kernel. */

@@ -33,7 +33,8 @@ import torch
 
 def masked_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                      softmax_scale: float, output_dtype: torch.dtype,
-                     is_causal: bool = True, alibi_slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     is_causal: bool = True, alibi_slopes: Optional[torch.Tensor] = None,
+                     sink_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of ``query [q, Hq, D]`` over ``key/value [k, Hkv, D]`` (test_pa_mtp.py:175-220).
 
     KV heads are repeated to the query heads, scores are fp32, the causal rule lets query row i
@@ -57,7 +58,15 @@ def masked_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor
         keep = torch.ones(ql, kl, dtype=torch.bool, device=query.device).tril(diagonal=kl - ql)
         bias.masked_fill_(keep.logical_not(), float("-inf"))
         scores += bias
-    weights = torch.softmax(scores, dim=-1)
+    if sink_tokens is None:
+        weights = torch.softmax(scores, dim=-1)
+    else:
+        # sink token per head: a weight exp(sink - max) in the denominator that carries no value
+        # (pa_decode_triton_gluon_fp8.py:1117-1123; the maximum is that of the real keys)
+        mx = scores.amax(dim=-1, keepdim=True)
+        e = torch.exp(scores - mx)
+        denom = e.sum(dim=-1, keepdim=True) + torch.exp(sink_tokens.float().view(-1, 1, 1) - mx)
+        weights = e / denom
     out = torch.einsum("hqk,khd->qhd", weights.float(), value.float())
     return out.to(output_dtype)
 
@@ -95,7 +104,8 @@ def paged_attention(query: torch.Tensor, key_cache: torch.Tensor, value_cache: t
                     query_indptr: torch.Tensor,
                     key_scale: Optional[torch.Tensor] = None,
                     value_scale: Optional[torch.Tensor] = None,
-                    alibi_slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    alibi_slopes: Optional[torch.Tensor] = None,
+                    sink_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The reference's paged multi-head attention (test_pa_mtp.py:223-291).
 
     query ``[total_q, Hq, D]`` split per sequence by ``query_indptr [S+1]``; caches in the paged
@@ -112,7 +122,7 @@ def paged_attention(query: torch.Tensor, key_cache: torch.Tensor, value_cache: t
         ctx = int(context_lens[s].item())
         keys, values = gather_sequence(k_flat, v_flat, block_tables[s], ctx, bs, key_scale, value_scale)
         outs.append(masked_attention(q_split[s], keys, values, softmax_scale, out_dtype, is_causal=True,
-                                     alibi_slopes=alibi_slopes))
+                                     alibi_slopes=alibi_slopes, sink_tokens=sink_tokens))
     return torch.cat(outs)
 
 

@@ -320,3 +320,24 @@ def test_alibi_slopes(heads, ql, bs, quant):
     assert_close(unpack_mtp(out, cfg.num_seqs, ql, hkv), ref, what="alibi")
     no_bias, _ = run_operator(inp)
     assert (unpack_mtp(out, cfg.num_seqs, ql, hkv).float() - no_bias.float()).abs().max() > 1e-2   # the bias matters
+
+
+@pytest.mark.parametrize("heads,ql,bs,kv", [((32, 8), 1, 16, "fp8"), ((16, 2), 2, 1024, "fp8"), ((8, 2), 1, 16, "bf16")])
+def test_sink_tokens(heads, ql, bs, kv):
+    """Sink logits join the softmax denominator in the reduce (pa_decode_triton_gluon_fp8.py:1117-1123)."""
+    from oracle import pa_oracle
+    from triton_op_b200 import paged_attention_decode
+    from triton_op_b200.inputs import DecodeConfig, make_inputs, unpack_mtp
+    hq, hkv = heads
+    cfg = DecodeConfig("sink", 3, hq, hkv, bs, ql, ("fixed", 1), kv_dtype=kv, quant="per_tensor" if kv == "fp8" else "none")
+    inp = make_inputs(cfg, seed=41, device=DEV, context_lens=torch.tensor([600, 1300, 40]))
+    sinks = torch.linspace(-1.0, 3.0, hq).to(DEV)
+    out = torch.full_like(inp.query, float("nan"))
+    paged_attention_decode(out, inp.query, inp.key_cache, inp.value_cache, inp.context_lens, inp.block_tables,
+                           inp.softmax_scale, ql, inp.max_context, torch.bfloat16, None, inp.key_scale,
+                           inp.value_scale, sink_tokens=sinks)
+    torch.cuda.synchronize()
+    ks, vs = inp.flat_scales()
+    ref = pa_oracle.paged_attention(inp.query_tokens, inp.key_cache, inp.value_cache, inp.block_tables, inp.context_lens,
+                                    inp.query_indptr(), ks, vs, sink_tokens=sinks)
+    assert_close(unpack_mtp(out, cfg.num_seqs, ql, hkv), ref, what="sink tokens")

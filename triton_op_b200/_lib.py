@@ -10,7 +10,7 @@ import os
 
 from .build import LIB_PATH
 
-PA_ABI_VERSION = 1
+PA_ABI_VERSION = 2
 
 PA_OK = 0
 PA_DT_BF16, PA_DT_E4M3FN = 0, 1
@@ -32,7 +32,7 @@ class PaDecodeParams(C.Structure):
         [("struct_size", C.c_uint32), ("abi_version", C.c_uint32)]
         + [(n, C.c_void_p) for n in (
             "out", "query", "key_cache", "value_cache", "block_tables", "context_lens",
-            "query_scale", "key_scale", "value_scale", "alibi_slopes",
+            "query_scale", "key_scale", "value_scale", "alibi_slopes", "sink_tokens",
             "exp_sums", "max_logits", "tmp_out", "status", "trace")]
         + [(n, C.c_int32) for n in (
             "num_seqs", "num_kv_heads", "query_group_size", "query_len", "head_size",

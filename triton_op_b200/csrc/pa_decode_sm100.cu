@@ -414,6 +414,8 @@ int launch_reduce(const PaDecodeParams* p, float* tri_m, float* tri_l, float* tr
   r.S = p->num_seqs;
   r.Hkv = p->num_kv_heads;
   r.eqG = p->query_group_size * p->query_len;
+  r.G = p->query_group_size;
+  r.sink = p->sink_tokens;
   r.partition_size = p->partition_size;
   r.max_partitions = p->max_partitions;
   const int64_t cap = (int64_t)p->max_blocks_per_seq * p->block_size;

@@ -20,10 +20,11 @@ struct ReduceParams {
   const float* max_logits;
   const uint8_t* tmp_out;       // bf16
   const int32_t* context_lens;
+  const float* sink;            // optional [Hkv*G]: sink logit per query head, added to the row's weight sum
   float* tri_m;                 // optional fp32 triples
   float* tri_l;
   float* tri_o;
-  int32_t S, Hkv, eqG, partition_size, max_partitions, ctx_cap;
+  int32_t S, Hkv, eqG, G, partition_size, max_partitions, ctx_cap;
   int64_t out_stride_seq, out_stride_head;
   int64_t ws_stride_seq, ws_stride_head, ws_stride_part;
   int64_t tmp_stride_seq, tmp_stride_head, tmp_stride_part, tmp_stride_row;
@@ -144,14 +145,22 @@ __global__ void __launch_bounds__(WPR == 16 ? 512 : 128) pa_reduce_kernel(const 
     }
     M = mx;
   }
+  // sink token: a weight without a value, relative to the same maximum (triples stay without it)
+  float Wout = W;
+  if (p.sink != nullptr && W > 0.f) Wout += expf(p.sink[head * p.G + r % p.G] - M);
   const float inv = W > 0.f ? 1.0f / W : 0.f;
+  const float inv_out = Wout > 0.f ? 1.0f / Wout : 0.f;
+  float res[4];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) acc[e] *= inv;
+  for (int e = 0; e < 4; ++e) {
+    res[e] = acc[e] * inv_out;
+    acc[e] *= inv;
+  }
 
   if (p.out) {
     uint2 o;
-    o.x = pack_bf16x2(acc[0], acc[1]);
-    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.x = pack_bf16x2(res[0], res[1]);
+    o.y = pack_bf16x2(res[2], res[3]);
     *reinterpret_cast<uint2*>(p.out + 2 * ((int64_t)seq * p.out_stride_seq +
                                            ((int64_t)head * p.eqG + r) * p.out_stride_head + 4 * lane)) = o;
   }

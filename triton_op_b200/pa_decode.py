@@ -136,7 +136,8 @@ def _tensor_key(t) -> tuple:
 
 def _params_key(output, query, key_cache, value_cache, sequence_lengths, block_tables, softmax_scale,
                 query_sequence_length, max_sequence_length, compute_type, query_scale, key_scale, value_scale,
-                alibi_slopes, partition_size, exp_sums, max_logits, tmp_output, status) -> Optional[tuple]:
+                alibi_slopes, partition_size, exp_sums, max_logits, tmp_output, status,
+                sink_tokens=None) -> Optional[tuple]:
     """Everything the parameter block depends on: addresses, shapes, strides, dtypes, scalars.
     A decode loop calls with the same tensors every step, and validating them and filling the
     60-field block costs more host time than a small batch takes on the GPU."""
@@ -145,7 +146,7 @@ def _params_key(output, query, key_cache, value_cache, sequence_lengths, block_t
                 str(compute_type), int(partition_size)) + tuple(
             _tensor_key(t) for t in (output, query, key_cache, value_cache, sequence_lengths, block_tables,
                                      query_scale, key_scale, value_scale, alibi_slopes, exp_sums, max_logits,
-                                     tmp_output, status))
+                                     tmp_output, status, sink_tokens))
     except Exception:     # unexpected argument types: take the validating path, which reports them
         return None
 
@@ -153,7 +154,7 @@ def _params_key(output, query, key_cache, value_cache, sequence_lengths, block_t
 def build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
                  softmax_scale: float, query_sequence_length: int, max_sequence_length: int,
                  compute_type, query_scale, key_scale, value_scale, alibi_slopes,
-                 partition_size: int, exp_sums, max_logits, tmp_output, status, tune
+                 partition_size: int, exp_sums, max_logits, tmp_output, status, tune, sink_tokens=None
                  ) -> Tuple[PaDecodeParams, tuple]:
     """Validated C parameter block for the arguments, from a small cache when the same tensors
     (addresses, shapes, strides, dtypes) and scalars were validated before."""
@@ -161,7 +162,8 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
     if tune is None:
         key = _params_key(output, query, key_cache, value_cache, sequence_lengths, block_tables, softmax_scale,
                           query_sequence_length, max_sequence_length, compute_type, query_scale, key_scale,
-                          value_scale, alibi_slopes, partition_size, exp_sums, max_logits, tmp_output, status)
+                          value_scale, alibi_slopes, partition_size, exp_sums, max_logits, tmp_output, status,
+                          sink_tokens)
         hit = _PARAM_CACHE.get(key) if key is not None else None
         if hit is not None:
             p, ws = hit
@@ -170,7 +172,7 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
     p, keep, cacheable = _build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
                                        softmax_scale, query_sequence_length, max_sequence_length, compute_type,
                                        query_scale, key_scale, value_scale, alibi_slopes, partition_size,
-                                       exp_sums, max_logits, tmp_output, status, tune)
+                                       exp_sums, max_logits, tmp_output, status, tune, sink_tokens)
     if key is not None and cacheable:
         if len(_PARAM_CACHE) >= 16:
             _PARAM_CACHE.clear()
@@ -181,7 +183,7 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
 def _build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
                  softmax_scale: float, query_sequence_length: int, max_sequence_length: int,
                  compute_type, query_scale, key_scale, value_scale, alibi_slopes,
-                 partition_size: int, exp_sums, max_logits, tmp_output, status, tune
+                 partition_size: int, exp_sums, max_logits, tmp_output, status, tune, sink_tokens=None
                  ) -> Tuple[PaDecodeParams, tuple, bool]:
     """Validates the arguments as the reference does and fills the C parameter block.
 
@@ -324,6 +326,11 @@ def _build_params(output, query, key_cache, value_cache, sequence_lengths, block
                 and alibi_slopes.numel() == num_kv_heads * group and alibi_slopes.is_contiguous()):
             _fail("alibi_slopes must be a contiguous fp32 tensor with one slope per query head on the output's device")
     p.alibi_slopes = alibi_slopes.data_ptr() if alibi_slopes is not None else None
+    if sink_tokens is not None:
+        if not (isinstance(sink_tokens, torch.Tensor) and sink_tokens.dtype == torch.float32 and sink_tokens.device == dev
+                and sink_tokens.numel() == num_kv_heads * group and sink_tokens.is_contiguous()):
+            _fail("sink_tokens must be a contiguous fp32 tensor with one logit per query head on the output's device")
+        p.sink_tokens = sink_tokens.data_ptr()
     p.exp_sums, p.max_logits, p.tmp_out = exp_sums.data_ptr(), max_logits.data_ptr(), tmp_output.data_ptr()
     p.status = status.data_ptr() if status is not None else None
     p.trace = tune["trace"].data_ptr() if tune and tune.get("trace") is not None else None
@@ -382,6 +389,7 @@ def paged_attention_decode(
     tmp_output: Optional[torch.Tensor] = None,
     status: Optional[torch.Tensor] = None,
     time_kernels: bool = False,
+    sink_tokens: Optional[torch.Tensor] = None,
     tune: Optional[dict] = None,
 ) -> Dict:
     """Paged-attention decode with a split-KV partition pass and a log-sum-exp reduce.
@@ -398,7 +406,10 @@ def paged_attention_decode(
     partition_size)`` -- when omitted they come from a per-shape cache, so the tensors in the
     returned dictionary are overwritten by the next call of the same shape; ``status``: optional
     int32 CUDA scalar the kernels OR ``PA_DEV_*`` bits into; ``time_kernels``: measure the two
-    kernels with CUDA events (synchronises; off by default so the call stays asynchronous).
+    kernels with CUDA events (synchronises; off by default so the call stays asynchronous);
+    ``sink_tokens``: fp32 ``[query heads]`` sink logits whose weight ``exp(sink - max)`` joins every
+    row's softmax denominator in the reduce (the reference's unused Gluon reduce,
+    pa_decode_triton_gluon_fp8.py:1117-1123).
 
     Returns the reference's dictionary (:1889-1897): ``triton_decode_time``,
     ``triton_reduce_time``, ``total_triton_time`` (microseconds; 0.0 unless ``time_kernels``),
@@ -407,7 +418,7 @@ def paged_attention_decode(
     p, keep = build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
                            softmax_scale, query_sequence_length, max_sequence_length, compute_type,
                            query_scale, key_scale, value_scale, alibi_slopes, partition_size,
-                           exp_sums, max_logits, tmp_output, status, tune)
+                           exp_sums, max_logits, tmp_output, status, tune, sink_tokens)
     if not output.is_cuda:
         raise RuntimeError("paged_attention_decode runs on CUDA tensors only; there is no CPU fallback")
     L = _lib.lib()
