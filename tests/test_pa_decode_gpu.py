@@ -341,3 +341,34 @@ def test_sink_tokens(heads, ql, bs, kv):
     ref = pa_oracle.paged_attention(inp.query_tokens, inp.key_cache, inp.value_cache, inp.block_tables, inp.context_lens,
                                     inp.query_indptr(), ks, vs, sink_tokens=sinks)
     assert_close(unpack_mtp(out, cfg.num_seqs, ql, hkv), ref, what="sink tokens")
+
+
+def test_operator_is_cuda_graph_capturable():
+    """No allocation, no synchronisation, launches on the current stream: a decode call (both kernels,
+    the reduce with its programmatic-launch attribute) can be captured once and replayed per step."""
+    from triton_op_b200 import paged_attention_decode
+    from triton_op_b200.inputs import DecodeConfig, make_inputs, unpack_mtp
+    cfg = DecodeConfig("graph", 4, 16, 2, 16, 2, ("fixed", 1), quant="per_token")
+    inp = make_inputs(cfg, seed=7, device=DEV, context_lens=torch.tensor([300, 1025, 16, 700]))
+    out = torch.zeros_like(inp.query)
+
+    def step():
+        paged_attention_decode(out, inp.query, inp.key_cache, inp.value_cache, inp.context_lens, inp.block_tables,
+                               inp.softmax_scale, 2, inp.max_context, torch.bfloat16, None, inp.key_scale, inp.value_scale)
+
+    step()                                   # creates the cached workspaces outside the capture
+    torch.cuda.synchronize()
+    eager = out.clone()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    # the graph reads lengths and tables from device memory at replay time: a shorter context changes the result
+    inp.context_lens[1] = 512
+    graph.replay()
+    torch.cuda.synchronize()
+    assert not torch.equal(out[1], eager[1]) and torch.equal(out[0], eager[0])
+    assert_close(unpack_mtp(out, 4, 2, 2), oracle_output(inp), what="graph replay after a length change")
