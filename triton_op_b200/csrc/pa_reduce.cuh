@@ -62,9 +62,10 @@ __global__ void __launch_bounds__(WPR == 16 ? 512 : 128) pa_reduce_kernel(const 
   // nothing that kernel wrote is read before this point.
   grid_dependency_wait();
 
-  // Partitions are taken 32 at a time (lane = partition for the max / weight, then eight
-  // partial-output rows in flight per step) with a running maximum, so a chunk costs about
-  // one global-memory round trip.
+  // Partitions are taken 32 at a time (lane = partition for the max / weight, then sixteen
+  // partial-output rows in flight per step) with a running maximum.  The first sixteen rows
+  // of a chunk are requested together with the maxima and sums, so the usual row (at most 16
+  // partitions) costs one memory round trip.
   float M = -INFINITY;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   float W = 0.f;
@@ -76,9 +77,10 @@ __global__ void __launch_bounds__(WPR == 16 ? 512 : 128) pa_reduce_kernel(const 
       m = p.max_logits[ws_base + (int64_t)pi * p.ws_stride_part];
       l = p.exp_sums[ws_base + (int64_t)pi * p.ws_stride_part];
     }
-    uint2 raw[8];  // first eight rows of the chunk are requested before the maximum is known
+    constexpr int kFlight = 16;
+    uint2 raw[kFlight];  // requested before the maximum is known
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < kFlight; ++j)
       raw[j] = j < cnt ? *reinterpret_cast<const uint2*>(p.tmp_out + 2 * (tmp_base + (int64_t)(p0 + j) * p.tmp_stride_part))
                        : make_uint2(0u, 0u);
     float cm = (l > 0.f) ? m : -INFINITY;
@@ -93,16 +95,16 @@ __global__ void __launch_bounds__(WPR == 16 ? 512 : 128) pa_reduce_kernel(const 
       M = newM;
     }
     const float w = (l > 0.f && m > -INFINITY) ? l * expf(m - M) : 0.f;
-    for (int j0 = 0; j0 < cnt; j0 += 8) {
+    for (int j0 = 0; j0 < cnt; j0 += kFlight) {
       if (j0 > 0) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < kFlight; ++j)
           raw[j] = (j0 + j) < cnt
                        ? *reinterpret_cast<const uint2*>(p.tmp_out + 2 * (tmp_base + (int64_t)(p0 + j0 + j) * p.tmp_stride_part))
                        : make_uint2(0u, 0u);
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < kFlight; ++j) {
         const float wj = __shfl_sync(kFullMask, w, (j0 + j) & 31);
         if ((j0 + j) < cnt && wj != 0.f) {  // a zero-weight partition may hold anything
           W += wj;
