@@ -497,11 +497,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     for (int i = 0; i < n_local && !dead; ++i) {
       const TcItem it = it_next;
       const int pid = clamp_page(pid_next, true);
-      if (i + 1 < n_local) {
-        cur.advance(p, seq_off);
-        it_next = cur.item(p, seq_off, seq_ctx);
-        pid_next = load_page_id(it_next);
-      }
       const int slot = i % NS;
       stamp(is_v ? 1 : 0, i, 0);
       if (i >= NS) {
@@ -550,6 +545,13 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         }
       }
       stamp(is_v ? 1 : 0, i, 2);
+      // the next item and its page id, after this item's copies are on their way (the load has
+      // the whole wait for the next slot to land)
+      if (i + 1 < n_local) {
+        cur.advance(p, seq_off);
+        it_next = cur.item(p, seq_off, seq_ctx);
+        pid_next = load_page_id(it_next);
+      }
     }
   } else
   if (warp == kWarpQ) {
