@@ -372,3 +372,40 @@ def test_operator_is_cuda_graph_capturable():
     torch.cuda.synchronize()
     assert not torch.equal(out[1], eager[1]) and torch.equal(out[0], eager[0])
     assert_close(unpack_mtp(out, 4, 2, 2), oracle_output(inp), what="graph replay after a length change")
+
+
+@pytest.mark.parametrize("name", ["cfg3_llama70b_mtp", "cfg4_longctx", "cfg5_serving_fp8", "cfg5_serving_bf16"])
+def test_baseline_configs_full_size_properties(name):
+    """The other baseline workloads at their full size.  The oracle checks a sample of sequences;
+    the rest is covered by properties that do not depend on the size: a sequence's rows do not
+    depend on which other sequences share the call (bit-identical in a sub-batch), and with a
+    constant value cache every output equals that constant times the value scale."""
+    import copy
+    from triton_op_b200.inputs import CONFIGS, make_inputs
+    cfg = CONFIGS[name]
+    inp = make_inputs(cfg, seed=0, device=DEV)
+    st = _status()
+    out, _ = run_operator(inp, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and bool(torch.isfinite(out.float()).all())
+    L = cfg.query_len
+    g = torch.Generator().manual_seed(1)
+    pick = sorted(torch.randperm(cfg.num_seqs, generator=g)[:min(6, cfg.num_seqs)].tolist())
+    sub = copy.copy(inp)
+    sub.cfg = type(cfg)(**{**cfg.__dict__, "num_seqs": len(pick)})
+    rows = [s * L + t for s in pick for t in range(L)]
+    sub.query_tokens = inp.query_tokens[rows]
+    sub.query = inp.query[pick]
+    sub.block_tables = inp.block_tables[pick]
+    sub.context_lens = inp.context_lens[pick]
+    assert_close(out[rows], oracle_output(sub), what=f"{name}: sampled sequences vs oracle")
+    out_sub, _ = run_operator(sub, status=st)
+    assert torch.equal(out_sub, out[rows])
+    if cfg.quant != "per_token":          # (per-token value scales differ by token: no constant output)
+        const = copy.copy(inp)
+        const.value_cache = torch.full_like(inp.value_cache.float(), 0.75).to(inp.value_cache.dtype)
+        out_c, _ = run_operator(const, status=st)
+        expect = 0.75 * (float(inp.value_scale) if inp.value_scale is not None else 1.0)
+        assert torch.allclose(out_c.float(), torch.full_like(out_c.float(), expect), rtol=1e-2, atol=0)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
