@@ -243,7 +243,7 @@ def run_ours(args, rank: int, world: int, local: int):
         plan = plan_kv_shards(inp.context_lens.tolist(), world, cfg.partition_size, cfg.query_len)[rank]
         decoder = KvShardedDecoder(inp.query, inp.key_cache, inp.value_cache, plan, inp.block_tables,
                                    inp.softmax_scale, inp.key_scale, inp.value_scale,
-                                   partition_size=cfg.partition_size, status=status)
+                                   partition_size=cfg.partition_size, status=status, exchange=args.exchange)
     c = inp.cfg
     out = torch.empty_like(inp.query) if decoder is None else decoder.out
 
@@ -401,8 +401,8 @@ def run_ours(args, rank: int, world: int, local: int):
                    "l2": "inputs larger than L2 (KV read per step: %.0f MB per GPU)" % (kv_bytes / 1e6),
                    "sharding": {"sequences-weak": "sequences, one full batch per GPU, no collective",
                                 "sequences-strong": "one batch, sequences dealt out by token count, no collective",
-                                "kv-partitions": "KV partition ranges per GPU; (max, sum, out) triples "
-                                                 "all-gathered over NCCL and merged"}[mode]},
+                                "kv-partitions": "KV partition ranges per GPU; (max, sum, out) triples exchanged ("
+                                                 + args.exchange + ") and merged"}[mode]},
         "roofline": {"bound": "hbm", "kernel": "partition kernel (pa_partition_sm100)", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind + " (torch copy_, read+write)", "unit": "GB/s", "frac": achieved / peak,
                      "us_per_launch": us_partition, "algorithmic_bytes": kv_bytes,
@@ -432,6 +432,8 @@ def main():
     ap.add_argument("--sharding", default="auto",
                     choices=["auto", "sequences-weak", "sequences-strong", "kv-partitions"],
                     help="multi-GPU split; auto = KV partitions for the long-context workload, else one batch per GPU")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="KV-partition sharding: triples exchanged by NVLink peer stores or by an NCCL all-gather")
     ap.add_argument("--no-graph", action="store_true", help="run the e2e step with eager launches instead of a CUDA graph")
     ap.add_argument("--num-seqs", type=int, default=0,
                     help="override the workload's batch size (profiler captures of the large workloads)")

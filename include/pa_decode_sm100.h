@@ -180,6 +180,48 @@ int pa_merge_packed_triples_sm100(void* out, int64_t out_stride_row, const float
                                   int32_t num_shards, int32_t num_rows, int32_t head_size, void* stream);
 
 /*
+ * The same exchange over NVLink peer stores instead of an all-gather (no counterpart in the
+ * reference).  Every rank owns a receive buffer of 2 * world_size * message_floats floats and
+ * world_size int32 flag words (zero before the first step), both mapped into its peers
+ * (pa_exchange_alloc / pa_exchange_open below, or any other peer mapping); `peer_recv[g]` /
+ * `peer_flags[g]` are rank g's buffers as this process's device addresses them (entry `rank` =
+ * the local ones).  One decode step `epoch` = 1, 2, ...:
+ *   pa_push_message_sm100  stores this rank's packed message (pa_packed_triple_floats floats, as
+ *                          pa_reduce_sm100 left it) into slot [epoch & 1][rank] of every rank's
+ *                          buffer and then raises flag[rank] = epoch everywhere;
+ *   pa_merge_wait_sm100    waits, bounded (about a second, then PA_DEV_WAIT_TIMEOUT in *status and
+ *                          no output), until all local flags have reached `epoch`, then merges the
+ *                          world_size messages of parity epoch & 1 into `out`.
+ * Ranks must call both once per step with the same epoch sequence.  `done_counter` is a local
+ * device int32, zero before the first call.
+ */
+/*
+ * Exchange memory that peers can map.  Such a buffer must be an allocation of its own (a handle
+ * names a whole allocation), and a peer must open the handle WITH ITS OWN DEVICE CURRENT: the
+ * mapping belongs to the opening device's address space, and kernels of another device of the
+ * same process cannot use it.
+ *   pa_exchange_alloc  allocates `bytes` of zeroed device memory on the current device and writes
+ *                      its 64-byte inter-process handle;
+ *   pa_exchange_open   maps a peer process's allocation into the current device (enabling peer
+ *                      access to the exporting device if needed) and reads one word of it through
+ *                      a host-side copy, so an unusable mapping is an error code here, not a
+ *                      fault in a kernel later;
+ *   pa_exchange_close  unmaps what pa_exchange_open returned (before the owner frees it);
+ *   pa_exchange_free   frees what pa_exchange_alloc returned.
+ */
+#define PA_IPC_HANDLE_BYTES 64
+int pa_exchange_alloc(int64_t bytes, void** ptr, uint8_t* handle);
+int pa_exchange_open(const uint8_t* handle, void** ptr);
+int pa_exchange_close(void* ptr);
+int pa_exchange_free(void* ptr);
+int pa_push_message_sm100(const float* message, int64_t message_floats, void* const* peer_recv,
+                          void* const* peer_flags, int32_t* done_counter, int32_t world_size, int32_t rank,
+                          int32_t epoch, void* stream);
+int pa_merge_wait_sm100(void* out, int64_t out_stride_row, const float* recv, const int32_t* flags,
+                        int32_t* status, int32_t world_size, int32_t epoch, int32_t num_rows,
+                        int32_t head_size, void* stream);
+
+/*
  * KV-cache write side (the step before the decode path; the reference builds its caches offline
  * with torch permutes, test_pa_mtp.py:109-172, and quantises them per token with
  * quantize_kv_cache_symmetric, :294-369): quantise T new key / value tokens and scatter them

@@ -19,10 +19,13 @@ PA_V_NORMAL, PA_V_TRANSPOSED = 0, 1
 PA_DEV_WAIT_TIMEOUT, PA_DEV_BAD_PAGE_ID, PA_DEV_CTX_TOO_LONG = 1, 2, 4
 PA_TRACE_WORDS = 8 * 64 * 4
 PA_NOALLOC_SCRATCH_BYTES = 16 << 20
+PA_IPC_HANDLE_BYTES = 64
 
 EXPORTS = (
     "pa_decode_sm100", "pa_decode_noalloc_sm100", "pa_partition_sm100", "pa_reduce_sm100", "pa_merge_triples_sm100",
-    "pa_merge_packed_triples_sm100", "pa_packed_triple_floats", "pa_cache_write_sm100", "pa_query_launch_sm100", "pa_strerror", "pa_last_cuda_error", "pa_abi_version",
+    "pa_merge_packed_triples_sm100", "pa_packed_triple_floats", "pa_exchange_alloc", "pa_exchange_open", "pa_exchange_close", "pa_exchange_free",
+    "pa_push_message_sm100", "pa_merge_wait_sm100",
+    "pa_cache_write_sm100", "pa_query_launch_sm100", "pa_strerror", "pa_last_cuda_error", "pa_abi_version",
 )
 
 
@@ -101,6 +104,18 @@ def lib() -> C.CDLL:
     L.pa_packed_triple_floats.argtypes = [C.c_int32, C.c_int32]
     L.pa_packed_triple_floats.restype = C.c_int64
     L.pa_query_launch_sm100.argtypes = [P] + [C.POINTER(C.c_int32)] * 4
+    L.pa_push_message_sm100.argtypes = [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p,
+                                        C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
+    L.pa_push_message_sm100.restype = C.c_int
+    L.pa_merge_wait_sm100.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                      C.c_int32, C.c_int32, C.c_void_p]
+    L.pa_merge_wait_sm100.restype = C.c_int
+    L.pa_exchange_alloc.argtypes = [C.c_int64, C.POINTER(C.c_void_p), C.c_char_p]
+    L.pa_exchange_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+    L.pa_exchange_close.argtypes = [C.c_void_p]
+    L.pa_exchange_free.argtypes = [C.c_void_p]
+    for name in ("pa_exchange_alloc", "pa_exchange_open", "pa_exchange_close", "pa_exchange_free"):
+        getattr(L, name).restype = C.c_int
     L.pa_cache_write_sm100.argtypes = [C.POINTER(PaCacheWriteParams), C.c_void_p]
     L.pa_cache_write_sm100.restype = C.c_int
     for name in ("pa_decode_sm100", "pa_decode_noalloc_sm100", "pa_partition_sm100", "pa_reduce_sm100",

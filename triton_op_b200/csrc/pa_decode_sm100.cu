@@ -14,6 +14,7 @@
 #include "pa_partition_tc.cuh"
 #include "pa_reduce.cuh"
 #include "pa_cache_write.cuh"
+#include "pa_exchange.cuh"
 
 namespace {
 
@@ -584,6 +585,114 @@ int pa_merge_packed_triples_sm100(void* out, int64_t out_stride_row, const float
   const int64_t o_off = stride - (int64_t)num_rows * head_size;
   return launch_merge(out, out_stride_row, packed, packed + num_rows, packed + o_off, num_shards, num_rows,
                       head_size, stride, stride, stream);
+}
+
+static_assert(sizeof(cudaIpcMemHandle_t) == PA_IPC_HANDLE_BYTES, "handle size is part of the ABI");
+
+int pa_exchange_alloc(int64_t bytes, void** ptr, uint8_t* handle) {
+  if (!ptr || !handle) return PA_ERR_NULL_POINTER;
+  if (bytes <= 0) return PA_ERR_BAD_SHAPE;
+  void* d = nullptr;
+  cudaError_t e = cudaMalloc(&d, (size_t)bytes);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaMemset(d, 0, (size_t)bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();   // zeroes are in place before anybody maps it
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, d);
+  if (e != cudaSuccess) {
+    cudaFree(d);
+    return cuda_fail(e);
+  }
+  memcpy(handle, &h, sizeof(h));
+  *ptr = d;
+  return PA_OK;
+}
+
+int pa_exchange_open(const uint8_t* handle, void** ptr) {
+  if (!ptr || !handle) return PA_ERR_NULL_POINTER;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void* d = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&d, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_fail(e);
+  // One word through a host-side copy: a mapping this device cannot use fails here with an error
+  // code (a copy does not poison the context the way a faulting kernel does).
+  int32_t word = 0;
+  e = cudaMemcpy(&word, d, sizeof(word), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) {
+    cudaIpcCloseMemHandle(d);
+    return cuda_fail(e);
+  }
+  *ptr = d;
+  return PA_OK;
+}
+
+int pa_exchange_close(void* ptr) {
+  if (!ptr) return PA_ERR_NULL_POINTER;
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? PA_OK : cuda_fail(e);
+}
+
+int pa_exchange_free(void* ptr) {
+  if (!ptr) return PA_ERR_NULL_POINTER;
+  cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? PA_OK : cuda_fail(e);
+}
+
+int pa_push_message_sm100(const float* message, int64_t message_floats, void* const* peer_recv,
+                          void* const* peer_flags, int32_t* done_counter, int32_t world_size, int32_t rank,
+                          int32_t epoch, void* stream) {
+  if (!message || !peer_recv || !peer_flags || !done_counter) return PA_ERR_NULL_POINTER;
+  if (world_size < 1 || world_size > pa::kMaxPeers || rank < 0 || rank >= world_size || epoch < 1 ||
+      message_floats <= 0 || (message_floats & 3))
+    return PA_ERR_BAD_SHAPE;
+  if (!aligned16(message)) return PA_ERR_ALIGNMENT;
+  pa::ExchangeParams k;
+  memset(&k, 0, sizeof(k));
+  k.msg = message;
+  for (int g = 0; g < world_size; ++g) {
+    if (!peer_recv[g] || !peer_flags[g]) return PA_ERR_NULL_POINTER;
+    if (!aligned16(peer_recv[g])) return PA_ERR_ALIGNMENT;
+    k.recv[g] = static_cast<float*>(peer_recv[g]);
+    k.flags[g] = static_cast<int*>(peer_flags[g]);
+  }
+  k.done = done_counter;
+  k.world = world_size;
+  k.rank = rank;
+  k.epoch = epoch;
+  k.msg_floats = message_floats;
+  const int64_t n16 = message_floats / 4;
+  int64_t blocks = (n16 + 255) / 256;
+  if (blocks > 64) blocks = 64;
+  pa::pa_push_message_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(k);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return PA_OK;
+}
+
+int pa_merge_wait_sm100(void* out, int64_t out_stride_row, const float* recv, const int32_t* flags,
+                        int32_t* status, int32_t world_size, int32_t epoch, int32_t num_rows,
+                        int32_t head_size, void* stream) {
+  if (!out || !recv || !flags) return PA_ERR_NULL_POINTER;
+  if (world_size < 1 || world_size > pa::kMaxPeers || epoch < 1 || num_rows < 0) return PA_ERR_BAD_SHAPE;
+  if (head_size != pa::kD) return PA_ERR_UNSUPPORTED;
+  if (!aligned16(recv) || (reinterpret_cast<uintptr_t>(out) & 7u) || (out_stride_row & 3)) return PA_ERR_ALIGNMENT;
+  if (num_rows == 0) return PA_OK;
+  pa::MergeWaitParams k;
+  memset(&k, 0, sizeof(k));
+  k.out = static_cast<uint8_t*>(out);
+  k.out_stride_row = out_stride_row;
+  k.recv = recv;
+  k.flags = flags;
+  k.status = status;
+  k.world = world_size;
+  k.epoch = epoch;
+  k.num_rows = num_rows;
+  k.msg_floats = pa_packed_triple_floats(num_rows, head_size);
+  pa::pa_merge_wait_kernel<<<(unsigned)((num_rows + 3) / 4), 128, 0, static_cast<cudaStream_t>(stream)>>>(k);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  return PA_OK;
 }
 
 int pa_cache_write_sm100(const PaCacheWriteParams* p, void* stream) {

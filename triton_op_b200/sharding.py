@@ -28,6 +28,7 @@ import torch
 __all__ = [
     "shard_sequences", "shard_token_counts", "KvShard", "plan_kv_shards", "local_block_table",
     "decode_kv_shard", "all_gather_triples", "merge_triples_cuda", "gather_and_merge", "KvShardedDecoder",
+    "PeerExchange",
 ]
 
 
@@ -260,6 +261,93 @@ def gather_and_merge(m: torch.Tensor, l: torch.Tensor, o: torch.Tensor, group=No
     return merge_triples_cuda(m_all, l_all, o_all, out)
 
 
+class PeerExchange:
+    """The triple exchange over NVLink peer stores instead of an all-gather.
+
+    Every rank owns a receive buffer (two parities x world x message) and one flag word per
+    source rank; the constructor maps all ranks' buffers into this rank's device through CUDA
+    IPC (ranks of one node, one process each).  Per decode step, :meth:`push` stores this rank's packed message into
+    every rank's buffer and raises its flag there, and :meth:`merge` waits (bounded) for all
+    flags of the step and merges.  Data only ever moves by stores into the consumer's memory.
+    """
+
+    def __init__(self, num_rows: int, head_size: int, device: torch.device, group=None):
+        import torch.distributed as dist
+        from . import _lib
+
+        self._lib = _lib
+        self._L = _lib.lib()
+        self.group = group
+        self.device = device
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.num_rows, self.head_size = num_rows, head_size
+        self.msg_floats = int(self._L.pa_packed_triple_floats(num_rows, head_size))
+        # one allocation of its own per rank (an inter-process handle names a whole allocation):
+        # recv [2][world][msg_floats] fp32, then the flag words [world] int32
+        self._flag_off = 4 * 2 * self.world * self.msg_floats
+        nbytes = self._flag_off + 4 * ((self.world + 3) // 4 * 4)
+        self.done = torch.zeros(1, dtype=torch.int32, device=device)
+        handle = C.create_string_buffer(_lib.PA_IPC_HANDLE_BYTES)
+        own = C.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(self._L.pa_exchange_alloc(nbytes, C.byref(own), handle), "pa_exchange_alloc")
+        self._own = own.value
+        everyone: List = [None] * self.world
+        dist.all_gather_object(everyone, handle.raw, group=group)
+        self._mapped: List[int] = []      # what close() has to unmap
+        bases = []
+        for g, raw in enumerate(everyone):
+            if g == self.rank:
+                bases.append(self._own)
+                continue
+            ptr = C.c_void_p()
+            with torch.cuda.device(device):   # the mapping belongs to the device that is current here
+                _lib.check(self._L.pa_exchange_open(raw, C.byref(ptr)), "pa_exchange_open")
+            self._mapped.append(ptr.value)
+            bases.append(ptr.value)
+        self._recv_ptrs = (C.c_void_p * self.world)(*bases)
+        self._flag_ptrs = (C.c_void_p * self.world)(*[b + self._flag_off for b in bases])
+        self.epoch = 0
+        dist.barrier(group)       # every rank has mapped every buffer before anybody pushes
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers, then (after every rank has done so) frees this rank's.
+        Collective: all ranks call it, with no step in flight."""
+        import torch.distributed as dist
+        if self._own is None:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for ptr in self._mapped:
+                self._lib.check(self._L.pa_exchange_close(ptr), "pa_exchange_close")
+            self._mapped = []
+            dist.barrier(self.group)
+            self._lib.check(self._L.pa_exchange_free(self._own), "pa_exchange_free")
+        self._own = None
+
+    def push(self, message: torch.Tensor) -> None:
+        """Next step: stores ``message`` (packed triples, fp32) everywhere and raises the flags."""
+        self.epoch += 1
+        with torch.cuda.device(message.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            self._lib.check(self._L.pa_push_message_sm100(message.data_ptr(), self.msg_floats, self._recv_ptrs,
+                                                          self._flag_ptrs, self.done.data_ptr(), self.world, self.rank,
+                                                          self.epoch, stream), "pa_push_message_sm100")
+
+    def merge(self, out: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Waits for the current step's messages of all ranks and merges them into ``out`` (bf16)."""
+        flat = out.view(-1, self.head_size)
+        with torch.cuda.device(out.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            self._lib.check(self._L.pa_merge_wait_sm100(flat.data_ptr(), flat.stride(0), self._own,
+                                                        self._own + self._flag_off,
+                                                        status.data_ptr() if status is not None else None,
+                                                        self.world, self.epoch, self.num_rows, self.head_size, stream),
+                            "pa_merge_wait_sm100")
+        return out
+
+
 class KvShardedDecoder:
     """One rank's side of KV-partition-sharded decode with everything per-batch prepared once.
 
@@ -275,7 +363,7 @@ class KvShardedDecoder:
     def __init__(self, query: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
                  shards: Sequence[KvShard], block_tables: torch.Tensor, softmax_scale: float,
                  key_scale, value_scale, *, partition_size: int = 256, group=None,
-                 status: Optional[torch.Tensor] = None):
+                 status: Optional[torch.Tensor] = None, exchange: str = "nccl"):
         import torch.distributed as dist
         from . import _lib
         from .pa_decode import build_params
@@ -311,6 +399,13 @@ class KvShardedDecoder:
             kinds[0] if kinds else 1, max(lens + [1]), None, None, key_scale, value_scale, None, partition_size,
             None, None, None, status, None)
         self.launches_per_step = 3
+        # the exchange: one NCCL all-gather, or peer stores over NVLink ("p2p", ranks of one node)
+        if exchange not in ("nccl", "p2p"):
+            raise ValueError("exchange must be 'nccl' or 'p2p'")
+        self.status = status
+        self.peer = PeerExchange(R, D, dev, group) if (exchange == "p2p" and self.world > 1) else None
+        if self.peer is not None:
+            self.launches_per_step = 4
 
     def step(self) -> torch.Tensor:
         """Launches one decode step on the current stream; returns the merged bf16 output
@@ -324,6 +419,9 @@ class KvShardedDecoder:
             lib.check(L.pa_partition_sm100(C.byref(self.params), stream), "pa_partition_sm100")
             lib.check(L.pa_reduce_sm100(C.byref(self.params), base, base + 4 * R, base + 4 * self._o_off, stream),
                       "pa_reduce_sm100")
+            if self.peer is not None:   # push to every rank's buffer, wait for theirs, merge
+                self.peer.push(self.msg)
+                return self.peer.merge(self.out, self.status)
             gathered = self.msg
             if self.world > 1:      # one collective per step
                 dist.all_gather_into_tensor(self.msg_all, self.msg, group=self.group)
