@@ -192,8 +192,10 @@ int pa_merge_packed_triples_sm100(void* out, int64_t out_stride_row, const float
  *   pa_merge_wait_sm100    waits, bounded (about a second, then PA_DEV_WAIT_TIMEOUT in *status and
  *                          no output), until all local flags have reached `epoch`, then merges the
  *                          world_size messages of parity epoch & 1 into `out`.
- * Ranks must call both once per step with the same epoch sequence.  `done_counter` is a local
- * device int32, zero before the first call.
+ * Ranks must call both once per step with the same epoch sequence.  `counters` is two local
+ * device int32 words, zero before the first call ([0] scratch, [1] = steps pushed so far).
+ * epoch = 0 in both calls means "the next step, counted on the device in counters[1]": the
+ * arguments are then the same every step, so the pair can be captured in a CUDA graph.
  */
 /*
  * Exchange memory that peers can map.  Such a buffer must be an allocation of its own (a handle
@@ -215,11 +217,11 @@ int pa_exchange_open(const uint8_t* handle, void** ptr);
 int pa_exchange_close(void* ptr);
 int pa_exchange_free(void* ptr);
 int pa_push_message_sm100(const float* message, int64_t message_floats, void* const* peer_recv,
-                          void* const* peer_flags, int32_t* done_counter, int32_t world_size, int32_t rank,
+                          void* const* peer_flags, int32_t* counters, int32_t world_size, int32_t rank,
                           int32_t epoch, void* stream);
 int pa_merge_wait_sm100(void* out, int64_t out_stride_row, const float* recv, const int32_t* flags,
-                        int32_t* status, int32_t world_size, int32_t epoch, int32_t num_rows,
-                        int32_t head_size, void* stream);
+                        const int32_t* counters, int32_t* status, int32_t world_size, int32_t epoch,
+                        int32_t num_rows, int32_t head_size, void* stream);
 
 /*
  * KV-cache write side (the step before the decode path; the reference builds its caches offline

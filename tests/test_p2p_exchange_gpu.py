@@ -48,6 +48,12 @@ def _rank_main(rank: int, world: int, port: int, ret):
             out = dec.step()
             torch.cuda.synchronize()
             worst = max(worst, float((out.float() - want).abs().max()))
+        graph = dec.capture()                   # the step number is counted on the device: replays stay in step
+        for _ in range(3):
+            dec.out.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            worst = max(worst, float((dec.out.float() - want).abs().max()))
         ret[f"err{rank}"] = worst
         ret[f"status{rank}"] = int(status.item())
         dist.barrier()

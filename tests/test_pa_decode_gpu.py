@@ -39,15 +39,17 @@ def test_partition_intermediates(name):
     cpu = golden_inputs(name)
     c = cpu.cfg
     ks, vs = cpu.flat_scales()
-    m_ref, l_ref, o_ref = pa_oracle.split_kv_partials(cpu.query, cpu.key_cache, cpu.value_cache, cpu.block_tables,
-                                                      cpu.context_lens, c.query_len, cpu.softmax_scale,
-                                                      c.partition_size, ks, vs)
     inp = cpu.to(DEV)
     _, res = run_operator(inp)
     torch.cuda.synchronize()
+    psize = res["partition_size"]        # 512 runs as 256-token sub-partitions on the operator's own workspaces
+    assert psize == 256
+    m_ref, l_ref, o_ref = pa_oracle.split_kv_partials(cpu.query, cpu.key_cache, cpu.value_cache, cpu.block_tables,
+                                                      cpu.context_lens, c.query_len, cpu.softmax_scale,
+                                                      psize, ks, vs)
     m, l, o = res["maximum_logits"].cpu(), res["exponential_sums"].cpu(), res["temporary_output"].float().cpu()
     for s in range(c.num_seqs):
-        np_s = (int(cpu.context_lens[s]) + c.partition_size - 1) // c.partition_size
+        np_s = (int(cpu.context_lens[s]) + psize - 1) // psize
         ms, ls, os_ = m[s, :, :np_s], l[s, :, :np_s], o[s, :, :np_s]
         mr, lr, orr = m_ref[s, :, :np_s], l_ref[s, :, :np_s], o_ref[s, :, :np_s]
         live = lr > 0
@@ -55,6 +57,32 @@ def test_partition_intermediates(name):
         assert torch.allclose(ms[live], mr[live], atol=1e-4, rtol=1e-5)
         assert torch.allclose(ls, lr, atol=1e-4, rtol=2e-4)
         assert torch.allclose(os_, orr, atol=6e-3, rtol=8e-3)
+
+
+def test_partition512_on_caller_workspaces_keeps_their_layout():
+    """Workspaces passed by the caller are filled at the partition size asked for (the mma.sync kernel)."""
+    from oracle import pa_oracle
+    cpu = golden_inputs("partition512")
+    c = cpu.cfg
+    ks, vs = cpu.flat_scales()
+    m_ref, l_ref, o_ref = pa_oracle.split_kv_partials(cpu.query, cpu.key_cache, cpu.value_cache, cpu.block_tables,
+                                                      cpu.context_lens, c.query_len, cpu.softmax_scale, 512, ks, vs)
+    inp = cpu.to(DEV)
+    P = (inp.max_context + 511) // 512
+    eqg = c.q_heads // c.kv_heads * c.query_len
+    shape = (c.num_seqs, c.kv_heads, P, eqg)
+    es = torch.zeros(shape, dtype=torch.float32, device=DEV)
+    ml = torch.zeros(shape, dtype=torch.float32, device=DEV)
+    tmp = torch.zeros(shape + (c.head_size,), dtype=torch.bfloat16, device=DEV)
+    got, res = run_operator(inp, exp_sums=es, max_logits=ml, tmp_output=tmp)
+    torch.cuda.synchronize()
+    assert res["partition_size"] == 512
+    assert_close(got, oracle_output(cpu), what="partition 512, caller workspaces")
+    for s in range(c.num_seqs):
+        np_s = (int(cpu.context_lens[s]) + 511) // 512
+        live = l_ref[s, :, :np_s] > 0
+        assert torch.allclose(ml[s, :, :np_s].cpu()[live], m_ref[s, :, :np_s][live], atol=1e-4, rtol=1e-5)
+        assert torch.allclose(es[s, :, :np_s].cpu(), l_ref[s, :, :np_s], atol=1e-4, rtol=2e-4)
 
 
 def test_workspaces_need_no_clearing_and_runs_are_bit_identical():

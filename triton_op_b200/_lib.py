@@ -107,8 +107,8 @@ def lib() -> C.CDLL:
     L.pa_push_message_sm100.argtypes = [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p,
                                         C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
     L.pa_push_message_sm100.restype = C.c_int
-    L.pa_merge_wait_sm100.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
-                                      C.c_int32, C.c_int32, C.c_void_p]
+    L.pa_merge_wait_sm100.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
+                                      C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
     L.pa_merge_wait_sm100.restype = C.c_int
     L.pa_exchange_alloc.argtypes = [C.c_int64, C.POINTER(C.c_void_p), C.c_char_p]
     L.pa_exchange_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]

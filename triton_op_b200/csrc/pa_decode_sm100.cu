@@ -643,7 +643,7 @@ int pa_push_message_sm100(const float* message, int64_t message_floats, void* co
                           void* const* peer_flags, int32_t* done_counter, int32_t world_size, int32_t rank,
                           int32_t epoch, void* stream) {
   if (!message || !peer_recv || !peer_flags || !done_counter) return PA_ERR_NULL_POINTER;
-  if (world_size < 1 || world_size > pa::kMaxPeers || rank < 0 || rank >= world_size || epoch < 1 ||
+  if (world_size < 1 || world_size > pa::kMaxPeers || rank < 0 || rank >= world_size || epoch < 0 ||
       message_floats <= 0 || (message_floats & 3))
     return PA_ERR_BAD_SHAPE;
   if (!aligned16(message)) return PA_ERR_ALIGNMENT;
@@ -671,10 +671,10 @@ int pa_push_message_sm100(const float* message, int64_t message_floats, void* co
 }
 
 int pa_merge_wait_sm100(void* out, int64_t out_stride_row, const float* recv, const int32_t* flags,
-                        int32_t* status, int32_t world_size, int32_t epoch, int32_t num_rows,
-                        int32_t head_size, void* stream) {
-  if (!out || !recv || !flags) return PA_ERR_NULL_POINTER;
-  if (world_size < 1 || world_size > pa::kMaxPeers || epoch < 1 || num_rows < 0) return PA_ERR_BAD_SHAPE;
+                        const int32_t* counters, int32_t* status, int32_t world_size, int32_t epoch,
+                        int32_t num_rows, int32_t head_size, void* stream) {
+  if (!out || !recv || !flags || (epoch == 0 && !counters)) return PA_ERR_NULL_POINTER;
+  if (world_size < 1 || world_size > pa::kMaxPeers || epoch < 0 || num_rows < 0) return PA_ERR_BAD_SHAPE;
   if (head_size != pa::kD) return PA_ERR_UNSUPPORTED;
   if (!aligned16(recv) || (reinterpret_cast<uintptr_t>(out) & 7u) || (out_stride_row & 3)) return PA_ERR_ALIGNMENT;
   if (num_rows == 0) return PA_OK;
@@ -684,6 +684,7 @@ int pa_merge_wait_sm100(void* out, int64_t out_stride_row, const float* recv, co
   k.out_stride_row = out_stride_row;
   k.recv = recv;
   k.flags = flags;
+  k.counters = counters;
   k.status = status;
   k.world = world_size;
   k.epoch = epoch;

@@ -29,16 +29,20 @@ struct ExchangeParams {
   const float* msg;                 // this rank's message, msg_floats floats (a multiple of 4)
   float* recv[kMaxPeers];           // rank g's receive buffer [2][world][msg_floats] (g == rank: the local one)
   int* flags[kMaxPeers];            // rank g's flag words [world]
-  int* done;                        // local scratch counter, zero between launches
+  int* done;                        // local: [0] CTA arrival count (zero between launches), [1] steps pushed so far
   int32_t* status;                  // optional
   int32_t world, rank, epoch;
   int64_t msg_floats;
 };
 
 __global__ void __launch_bounds__(256) pa_push_message_kernel(const __grid_constant__ ExchangeParams p) {
+  // epoch 0: the step number lives on the device (a captured launch replays with the same
+  // arguments).  done[1] only changes after every CTA has counted itself in, below.
+  int epoch = p.epoch;
+  if (epoch == 0) epoch = *reinterpret_cast<volatile int*>(p.done + 1) + 1;
   const int64_t n16 = p.msg_floats / 4;
   const float4* src = reinterpret_cast<const float4*>(p.msg);
-  const int64_t slot = ((int64_t)(p.epoch & 1) * p.world + p.rank) * p.msg_floats;
+  const int64_t slot = ((int64_t)(epoch & 1) * p.world + p.rank) * p.msg_floats;
   for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < n16; v += (int64_t)gridDim.x * blockDim.x) {
     const float4 x = src[v];
     for (int g = 0; g < p.world; ++g) reinterpret_cast<float4*>(p.recv[g] + slot)[v] = x;
@@ -49,10 +53,11 @@ __global__ void __launch_bounds__(256) pa_push_message_kernel(const __grid_const
   __syncthreads();
   if (threadIdx.x == 0) {
     if (atomicAdd(p.done, 1) == (int)gridDim.x - 1) {
-      *p.done = 0;
+      p.done[0] = 0;
+      p.done[1] = epoch;
       __threadfence_system();
       for (int g = 0; g < p.world; ++g) {
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flags[g] + p.rank), "r"(p.epoch) : "memory");
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flags[g] + p.rank), "r"(epoch) : "memory");
       }
     }
   }
@@ -63,6 +68,7 @@ struct MergeWaitParams {
   int64_t out_stride_row;
   const float* recv;                // local receive buffer [2][world][msg_floats]
   const int* flags;                 // local flag words [world]
+  const int* counters;              // the push kernel's counters (epoch 0: step number = counters[1])
   int32_t* status;                  // optional
   int32_t world, epoch, num_rows;
   int64_t msg_floats;
@@ -71,6 +77,7 @@ struct MergeWaitParams {
 // One warp per output row, four rows per CTA.
 __global__ void __launch_bounds__(128) pa_merge_wait_kernel(const __grid_constant__ MergeWaitParams p) {
   __shared__ int s_ok;
+  const int epoch = p.epoch ? p.epoch : p.counters[1];   // written by the push launched before this one
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   if ((int)threadIdx.x < p.world) {
@@ -79,7 +86,7 @@ __global__ void __launch_bounds__(128) pa_merge_wait_kernel(const __grid_constan
     for (uint32_t poll = 0; poll < (1u << 20); ++poll) {
       int f;
       asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(f) : "l"(p.flags + threadIdx.x) : "memory");
-      if (f >= p.epoch) { ok = true; break; }
+      if (f >= epoch) { ok = true; break; }
       __nanosleep(200);
     }
     if (!ok) s_ok = 0;
@@ -92,7 +99,7 @@ __global__ void __launch_bounds__(128) pa_merge_wait_kernel(const __grid_constan
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (row >= p.num_rows) return;
-  const float* base = p.recv + (int64_t)(p.epoch & 1) * p.world * p.msg_floats;
+  const float* base = p.recv + (int64_t)(epoch & 1) * p.world * p.msg_floats;
   const int64_t o_off = p.msg_floats - (int64_t)p.num_rows * kD;
   float M = -INFINITY;
   for (int s = 0; s < p.world; ++s) {

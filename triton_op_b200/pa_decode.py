@@ -297,6 +297,14 @@ def _build_params(output, query, key_cache, value_cache, sequence_lengths, block
                 _fail("per-token kv scales must be contiguous along block_size and share strides")
 
     # ---- workspaces
+    # The tcgen05 kernel works on 256-token partitions.  A larger partition size that is a multiple
+    # of 256 is run as 256-token sub-partitions when the workspaces are the operator's own (their
+    # layout is then nobody else's business; the output is the same attention, split finer).
+    # Workspaces passed by the caller keep the layout the caller asked for.
+    own_workspaces = exp_sums is None and max_logits is None and tmp_output is None
+    if (own_workspaces and partition_size > SEQUENCE_PARTITION_SIZE and partition_size % SEQUENCE_PARTITION_SIZE == 0
+            and kv_dtype == _lib.PA_DT_E4M3FN and not (tune and tune.get("warps"))):
+        partition_size = SEQUENCE_PARTITION_SIZE
     max_partitions = max(1, (int(max_sequence_length) + partition_size - 1) // partition_size)
     if exp_sums is None or max_logits is None or tmp_output is None:
         ws = get_workspaces(num_seqs, num_kv_heads, max_partitions, eq_group, head_size, output.dtype, dev)
@@ -413,7 +421,9 @@ def paged_attention_decode(
 
     Returns the reference's dictionary (:1889-1897): ``triton_decode_time``,
     ``triton_reduce_time``, ``total_triton_time`` (microseconds; 0.0 unless ``time_kernels``),
-    ``temporary_output``, ``final_output``, ``exponential_sums``, ``maximum_logits``.
+    ``temporary_output``, ``final_output``, ``exponential_sums``, ``maximum_logits``; plus
+    ``partition_size``, the split the returned workspaces hold: a requested multiple of 256 runs
+    as 256-token sub-partitions unless the caller passed workspaces of its own.
     """
     p, keep = build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
                            softmax_scale, query_sequence_length, max_sequence_length, compute_type,
@@ -445,6 +455,7 @@ def paged_attention_decode(
         "exponential_sums": keep[10],
         "maximum_logits": keep[11],
         "total_triton_time": decode_us + reduce_us,
+        "partition_size": int(p.partition_size),   # the split the workspaces hold (256 for multiples of 256)
     }
 
 

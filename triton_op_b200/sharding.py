@@ -287,7 +287,7 @@ class PeerExchange:
         # recv [2][world][msg_floats] fp32, then the flag words [world] int32
         self._flag_off = 4 * 2 * self.world * self.msg_floats
         nbytes = self._flag_off + 4 * ((self.world + 3) // 4 * 4)
-        self.done = torch.zeros(1, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(2, dtype=torch.int32, device=device)   # [1]: steps pushed, counted on the device
         handle = C.create_string_buffer(_lib.PA_IPC_HANDLE_BYTES)
         own = C.c_void_p()
         with torch.cuda.device(device):
@@ -308,7 +308,6 @@ class PeerExchange:
             bases.append(ptr.value)
         self._recv_ptrs = (C.c_void_p * self.world)(*bases)
         self._flag_ptrs = (C.c_void_p * self.world)(*[b + self._flag_off for b in bases])
-        self.epoch = 0
         dist.barrier(group)       # every rank has mapped every buffer before anybody pushes
 
     def close(self) -> None:
@@ -327,13 +326,13 @@ class PeerExchange:
         self._own = None
 
     def push(self, message: torch.Tensor) -> None:
-        """Next step: stores ``message`` (packed triples, fp32) everywhere and raises the flags."""
-        self.epoch += 1
+        """Next step: stores ``message`` (packed triples, fp32) everywhere and raises the flags.
+        The step number is counted on the device, so push + merge can be captured in a CUDA graph."""
         with torch.cuda.device(message.device):
             stream = torch.cuda.current_stream().cuda_stream
             self._lib.check(self._L.pa_push_message_sm100(message.data_ptr(), self.msg_floats, self._recv_ptrs,
-                                                          self._flag_ptrs, self.done.data_ptr(), self.world, self.rank,
-                                                          self.epoch, stream), "pa_push_message_sm100")
+                                                          self._flag_ptrs, self.counters.data_ptr(), self.world, self.rank,
+                                                          0, stream), "pa_push_message_sm100")
 
     def merge(self, out: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Waits for the current step's messages of all ranks and merges them into ``out`` (bf16)."""
@@ -341,9 +340,9 @@ class PeerExchange:
         with torch.cuda.device(out.device):
             stream = torch.cuda.current_stream().cuda_stream
             self._lib.check(self._L.pa_merge_wait_sm100(flat.data_ptr(), flat.stride(0), self._own,
-                                                        self._own + self._flag_off,
+                                                        self._own + self._flag_off, self.counters.data_ptr(),
                                                         status.data_ptr() if status is not None else None,
-                                                        self.world, self.epoch, self.num_rows, self.head_size, stream),
+                                                        self.world, 0, self.num_rows, self.head_size, stream),
                             "pa_merge_wait_sm100")
         return out
 
@@ -406,6 +405,17 @@ class KvShardedDecoder:
         self.peer = PeerExchange(R, D, dev, group) if (exchange == "p2p" and self.world > 1) else None
         if self.peer is not None:
             self.launches_per_step = 4
+
+    def capture(self) -> "torch.cuda.CUDAGraph":
+        """One step captured in a CUDA graph (collective: every rank calls it).  The launches of a
+        step take the same arguments every time (the peer exchange counts its steps on the
+        device), and four short kernels per step are otherwise bound by the host's launch rate."""
+        self.step()                       # anything lazy (communicator set-up) happens outside the capture
+        torch.cuda.synchronize(self.query.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.step()
+        return graph
 
     def step(self) -> torch.Tensor:
         """Launches one decode step on the current stream; returns the merged bf16 output
