@@ -269,7 +269,7 @@ def run_ours(args, rank: int, world: int, local: int):
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
     # ---- device-resident inputs: K steps between two events on the launching stream.
-    # The KV-partition-sharded step is four short launches; replayed as one CUDA graph, or the
+    # The KV-partition-sharded step is three short launches; replayed as one CUDA graph, or the
     # host's launch rate is what gets timed.
     step_graph = None
     if decoder is not None and not args.no_graph:

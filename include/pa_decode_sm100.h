@@ -181,22 +181,29 @@ int pa_merge_packed_triples_sm100(void* out, int64_t out_stride_row, const float
 
 /*
  * The same exchange over NVLink peer stores instead of an all-gather (no counterpart in the
- * reference).  Every rank owns a receive buffer of 2 * world_size * message_floats floats and
- * world_size int32 flag words (zero before the first step), both mapped into its peers
- * (pa_exchange_alloc / pa_exchange_open below, or any other peer mapping); `peer_recv[g]` /
- * `peer_flags[g]` are rank g's buffers as this process's device addresses them (entry `rank` =
- * the local ones).  One decode step `epoch` = 1, 2, ...:
- *   pa_push_message_sm100  stores this rank's packed message (pa_packed_triple_floats floats, as
- *                          pa_reduce_sm100 left it) into slot [epoch & 1][rank] of every rank's
- *                          buffer and then raises flag[rank] = epoch everywhere;
- *   pa_merge_wait_sm100    waits, bounded (about a second, then PA_DEV_WAIT_TIMEOUT in *status and
- *                          no output), until all local flags have reached `epoch`, then merges the
- *                          world_size messages of parity epoch & 1 into `out`.
- * Ranks must call both once per step with the same epoch sequence.  `counters` is two local
- * device int32 words, zero before the first call ([0] scratch, [1] = steps pushed so far).
- * epoch = 0 in both calls means "the next step, counted on the device in counters[1]": the
- * arguments are then the same every step, so the pair can be captured in a CUDA graph.
+ * reference).  Every rank owns a receive buffer of pa_exchange_bytes(world_size, num_rows,
+ * head_size) bytes, zero before the first step and mapped into its peers (pa_exchange_alloc /
+ * pa_exchange_open below, or any other peer mapping); `peer_recv[g]` is rank g's buffer as this
+ * process's device addresses it (entry `rank` = the local one).  It holds [2][world_size]
+ * [num_rows] triples as 16-byte lines {value, step, value, step}: the step number travels inside
+ * every 8-byte half, so the data needs no fence and no separate flag.  One decode step = 1, 2, ...:
+ *   pa_reduce_push_sm100  pa_reduce_sm100 without the bf16 output: stores each row's (m, l, o) into
+ *                         slot [step & 1][rank] of every rank's buffer;
+ *   pa_merge_wait_sm100   merges the world_size triples of each row from the local buffer into
+ *                         `out`, waiting, bounded (about a second, then PA_DEV_WAIT_TIMEOUT in
+ *                         *status and no output for that row), for lines not yet of this step.
+ * Ranks must call both once per step with the same step sequence.  step = 0 in both calls means
+ * "the next step, counted on the device": `counters` is then two local device int32 words, zero
+ * before the first call ([0] scratch, [1] = steps merged so far), and the arguments are the
+ * same every step, so the pair can be captured in a CUDA graph.
  */
+int64_t pa_exchange_bytes(int32_t world_size, int32_t num_rows, int32_t head_size);
+int pa_reduce_push_sm100(const PaDecodeParams* params, void* const* peer_recv, const int32_t* counters,
+                         int32_t world_size, int32_t rank, int32_t step, void* stream);
+int pa_merge_wait_sm100(void* out, int64_t out_stride_row, const void* recv, int32_t* counters,
+                        int32_t* status, int32_t world_size, int32_t step, int32_t num_rows,
+                        int32_t head_size, void* stream);
+
 /*
  * Exchange memory that peers can map.  Such a buffer must be an allocation of its own (a handle
  * names a whole allocation), and a peer must open the handle WITH ITS OWN DEVICE CURRENT: the
@@ -216,12 +223,6 @@ int pa_exchange_alloc(int64_t bytes, void** ptr, uint8_t* handle);
 int pa_exchange_open(const uint8_t* handle, void** ptr);
 int pa_exchange_close(void* ptr);
 int pa_exchange_free(void* ptr);
-int pa_push_message_sm100(const float* message, int64_t message_floats, void* const* peer_recv,
-                          void* const* peer_flags, int32_t* counters, int32_t world_size, int32_t rank,
-                          int32_t epoch, void* stream);
-int pa_merge_wait_sm100(void* out, int64_t out_stride_row, const float* recv, const int32_t* flags,
-                        const int32_t* counters, int32_t* status, int32_t world_size, int32_t epoch,
-                        int32_t num_rows, int32_t head_size, void* stream);
 
 /*
  * KV-cache write side (the step before the decode path; the reference builds its caches offline

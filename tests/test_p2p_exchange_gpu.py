@@ -1,6 +1,6 @@
 """The NVLink peer-store exchange of KV-partition-sharded decode, on two GPUs of one node (skipped
-with fewer).  Every rank decodes its ranges, pushes its triples into both ranks' buffers and
-merges; both must end up with the single-GPU result.  A second case leaves one rank's push out
+with fewer).  Every rank decodes its ranges, its reduce stores the triples into both ranks' buffers, and
+both merge; both must end up with the single-GPU result.  A second case leaves one rank's push out
 and checks that the other's bounded wait gives up with PA_DEV_WAIT_TIMEOUT instead of hanging."""
 from __future__ import annotations
 
@@ -61,7 +61,7 @@ def _rank_main(rank: int, world: int, port: int, ret):
         ex = PeerExchange(dec._rows, 128, dev)
         st2 = torch.zeros(1, dtype=torch.int32, device=dev)
         if rank == 0:
-            ex.push(dec.msg)
+            ex.reduce_push(dec.params)
             ex.merge(dec.out, st2)
             torch.cuda.synchronize()
             ret["timeout_status"] = int(st2.item())

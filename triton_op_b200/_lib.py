@@ -24,7 +24,7 @@ PA_IPC_HANDLE_BYTES = 64
 EXPORTS = (
     "pa_decode_sm100", "pa_decode_noalloc_sm100", "pa_partition_sm100", "pa_reduce_sm100", "pa_merge_triples_sm100",
     "pa_merge_packed_triples_sm100", "pa_packed_triple_floats", "pa_exchange_alloc", "pa_exchange_open", "pa_exchange_close", "pa_exchange_free",
-    "pa_push_message_sm100", "pa_merge_wait_sm100",
+    "pa_exchange_bytes", "pa_reduce_push_sm100", "pa_merge_wait_sm100",
     "pa_cache_write_sm100", "pa_query_launch_sm100", "pa_strerror", "pa_last_cuda_error", "pa_abi_version",
 )
 
@@ -104,11 +104,12 @@ def lib() -> C.CDLL:
     L.pa_packed_triple_floats.argtypes = [C.c_int32, C.c_int32]
     L.pa_packed_triple_floats.restype = C.c_int64
     L.pa_query_launch_sm100.argtypes = [P] + [C.POINTER(C.c_int32)] * 4
-    L.pa_push_message_sm100.argtypes = [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p,
-                                        C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
-    L.pa_push_message_sm100.restype = C.c_int
-    L.pa_merge_wait_sm100.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32,
-                                      C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
+    L.pa_exchange_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+    L.pa_exchange_bytes.restype = C.c_int64
+    L.pa_reduce_push_sm100.argtypes = [P, C.POINTER(C.c_void_p), C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]
+    L.pa_reduce_push_sm100.restype = C.c_int
+    L.pa_merge_wait_sm100.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32,
+                                      C.c_int32, C.c_int32, C.c_void_p]
     L.pa_merge_wait_sm100.restype = C.c_int
     L.pa_exchange_alloc.argtypes = [C.c_int64, C.POINTER(C.c_void_p), C.c_char_p]
     L.pa_exchange_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]

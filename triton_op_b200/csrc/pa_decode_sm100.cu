@@ -400,10 +400,23 @@ int launch_partition(const LaunchPlan& plan, cudaStream_t stream) {
   return PA_ERR_UNSUPPORTED;
 }
 
+struct PushTarget {   // where the reduce kernel also sends its triples (KV-partition sharding)
+  void* const* peer_recv;
+  const int32_t* counters;
+  int32_t world, rank, step;
+};
+
 int launch_reduce(const PaDecodeParams* p, float* tri_m, float* tri_l, float* tri_o,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const PushTarget* push = nullptr) {
   pa::ReduceParams r;
   memset(&r, 0, sizeof(r));
+  if (push) {
+    for (int g = 0; g < push->world; ++g) r.push[g] = static_cast<uint4*>(push->peer_recv[g]);
+    r.push_counter = push->counters;
+    r.push_world = push->world;
+    r.push_rank = push->rank;
+    r.push_step = push->step;
+  }
   r.out = static_cast<uint8_t*>(p->out);
   r.exp_sums = p->exp_sums;
   r.max_logits = p->max_logits;
@@ -639,42 +652,33 @@ int pa_exchange_free(void* ptr) {
   return e == cudaSuccess ? PA_OK : cuda_fail(e);
 }
 
-int pa_push_message_sm100(const float* message, int64_t message_floats, void* const* peer_recv,
-                          void* const* peer_flags, int32_t* done_counter, int32_t world_size, int32_t rank,
-                          int32_t epoch, void* stream) {
-  if (!message || !peer_recv || !peer_flags || !done_counter) return PA_ERR_NULL_POINTER;
-  if (world_size < 1 || world_size > pa::kMaxPeers || rank < 0 || rank >= world_size || epoch < 0 ||
-      message_floats <= 0 || (message_floats & 3))
-    return PA_ERR_BAD_SHAPE;
-  if (!aligned16(message)) return PA_ERR_ALIGNMENT;
-  pa::ExchangeParams k;
-  memset(&k, 0, sizeof(k));
-  k.msg = message;
-  for (int g = 0; g < world_size; ++g) {
-    if (!peer_recv[g] || !peer_flags[g]) return PA_ERR_NULL_POINTER;
-    if (!aligned16(peer_recv[g])) return PA_ERR_ALIGNMENT;
-    k.recv[g] = static_cast<float*>(peer_recv[g]);
-    k.flags[g] = static_cast<int*>(peer_flags[g]);
-  }
-  k.done = done_counter;
-  k.world = world_size;
-  k.rank = rank;
-  k.epoch = epoch;
-  k.msg_floats = message_floats;
-  const int64_t n16 = message_floats / 4;
-  int64_t blocks = (n16 + 255) / 256;
-  if (blocks > 64) blocks = 64;
-  pa::pa_push_message_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(k);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail(e);
-  return PA_OK;
+int64_t pa_exchange_bytes(int32_t world_size, int32_t num_rows, int32_t head_size) {
+  if (world_size < 1 || num_rows < 0 || head_size != pa::kD) return 0;
+  return 2 * (int64_t)world_size * num_rows * pa::kLinesPerRow * 16;
 }
 
-int pa_merge_wait_sm100(void* out, int64_t out_stride_row, const float* recv, const int32_t* flags,
-                        const int32_t* counters, int32_t* status, int32_t world_size, int32_t epoch,
-                        int32_t num_rows, int32_t head_size, void* stream) {
-  if (!out || !recv || !flags || (epoch == 0 && !counters)) return PA_ERR_NULL_POINTER;
-  if (world_size < 1 || world_size > pa::kMaxPeers || epoch < 0 || num_rows < 0) return PA_ERR_BAD_SHAPE;
+int pa_reduce_push_sm100(const PaDecodeParams* params, void* const* peer_recv, const int32_t* counters,
+                         int32_t world_size, int32_t rank, int32_t step, void* stream) {
+  int rc = validate(params, false, false);
+  if (rc != PA_OK) return rc;
+  if (!peer_recv || (step == 0 && !counters)) return PA_ERR_NULL_POINTER;
+  if (world_size < 1 || world_size > pa::kMaxPeers || rank < 0 || rank >= world_size || step < 0)
+    return PA_ERR_BAD_SHAPE;
+  for (int g = 0; g < world_size; ++g) {
+    if (!peer_recv[g]) return PA_ERR_NULL_POINTER;
+    if (!aligned16(peer_recv[g])) return PA_ERR_ALIGNMENT;
+  }
+  PaDecodeParams q = *params;
+  q.out = nullptr;   // this rank's output alone means nothing; the merge writes the result
+  PushTarget t = {peer_recv, counters, world_size, rank, step};
+  return launch_reduce(&q, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), &t);
+}
+
+int pa_merge_wait_sm100(void* out, int64_t out_stride_row, const void* recv, int32_t* counters,
+                        int32_t* status, int32_t world_size, int32_t step, int32_t num_rows,
+                        int32_t head_size, void* stream) {
+  if (!out || !recv || (step == 0 && !counters)) return PA_ERR_NULL_POINTER;
+  if (world_size < 1 || world_size > pa::kMaxPeers || step < 0 || num_rows < 0) return PA_ERR_BAD_SHAPE;
   if (head_size != pa::kD) return PA_ERR_UNSUPPORTED;
   if (!aligned16(recv) || (reinterpret_cast<uintptr_t>(out) & 7u) || (out_stride_row & 3)) return PA_ERR_ALIGNMENT;
   if (num_rows == 0) return PA_OK;
@@ -682,14 +686,12 @@ int pa_merge_wait_sm100(void* out, int64_t out_stride_row, const float* recv, co
   memset(&k, 0, sizeof(k));
   k.out = static_cast<uint8_t*>(out);
   k.out_stride_row = out_stride_row;
-  k.recv = recv;
-  k.flags = flags;
+  k.recv = static_cast<const uint4*>(recv);
   k.counters = counters;
   k.status = status;
   k.world = world_size;
-  k.epoch = epoch;
+  k.step = step;
   k.num_rows = num_rows;
-  k.msg_floats = pa_packed_triple_floats(num_rows, head_size);
   pa::pa_merge_wait_kernel<<<(unsigned)((num_rows + 3) / 4), 128, 0, static_cast<cudaStream_t>(stream)>>>(k);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);

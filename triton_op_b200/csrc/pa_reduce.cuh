@@ -14,6 +14,24 @@
 
 namespace pa {
 
+// Triples that cross GPUs travel as flagged 16-byte lines {value, step, value, step}: each
+// 8-byte half is written and read as a unit, so a reader that finds the step number it waits
+// for in both halves has the values too -- no fence, no separate flag, one trip over the link.
+// A row's triple is 1 + kD / 2 lines: {m, l}, then {o[2i], o[2i+1]}.
+constexpr int kMaxPeers = 16;
+constexpr int kLinesPerRow = 1 + kD / 2;
+
+__device__ __forceinline__ void st_line(uint4* dst, float a, float b, int step) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(__float_as_uint(a)), "r"(step),
+               "r"(__float_as_uint(b)), "r"(step)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_line(const uint4* src) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+  return v;
+}
+
 struct ReduceParams {
   uint8_t* out;                 // bf16 [S, Hkv*eqG, D]; may be null when triples are stored
   const float* exp_sums;
@@ -24,6 +42,11 @@ struct ReduceParams {
   float* tri_m;                 // optional fp32 triples
   float* tri_l;
   float* tri_o;
+  // optional: the triples also go, as flagged lines, into slot [step & 1][push_rank] of every
+  // rank's receive buffer [2][push_world][rows][kLinesPerRow] (entry push_rank: the local one)
+  uint4* push[kMaxPeers];
+  const int32_t* push_counter;  // push_step == 0: the step is push_counter[1] + 1 (steps merged so far, + 1)
+  int32_t push_world, push_rank, push_step;
   int32_t S, Hkv, eqG, G, partition_size, max_partitions, ctx_cap;
   int64_t out_stride_seq, out_stride_head;
   int64_t ws_stride_seq, ws_stride_head, ws_stride_part;
@@ -173,6 +196,16 @@ __global__ void __launch_bounds__(WPR == 16 ? 512 : 128) pa_reduce_kernel(const 
     }
     *reinterpret_cast<float4*>(p.tri_o + row * kD + 4 * lane) =
         make_float4(acc[0], acc[1], acc[2], acc[3]);
+  }
+  if (p.push_world > 0) {
+    const int step = p.push_step ? p.push_step : p.push_counter[1] + 1;
+    const int64_t line0 = (((int64_t)(step & 1) * p.push_world + p.push_rank) * n_rows + row) * kLinesPerRow;
+    for (int g = 0; g < p.push_world; ++g) {
+      uint4* dst = p.push[g] + line0;
+      if (lane == 0) st_line(dst, M, W, step);
+      st_line(dst + 1 + 2 * lane, acc[0], acc[1], step);
+      st_line(dst + 2 + 2 * lane, acc[2], acc[3], step);
+    }
   }
 }
 

@@ -264,11 +264,13 @@ def gather_and_merge(m: torch.Tensor, l: torch.Tensor, o: torch.Tensor, group=No
 class PeerExchange:
     """The triple exchange over NVLink peer stores instead of an all-gather.
 
-    Every rank owns a receive buffer (two parities x world x message) and one flag word per
-    source rank; the constructor maps all ranks' buffers into this rank's device through CUDA
-    IPC (ranks of one node, one process each).  Per decode step, :meth:`push` stores this rank's packed message into
-    every rank's buffer and raises its flag there, and :meth:`merge` waits (bounded) for all
-    flags of the step and merges.  Data only ever moves by stores into the consumer's memory.
+    Every rank owns a receive buffer (two parities x world x rows of flagged 16-byte lines); the
+    constructor maps all ranks' buffers into this rank's device through CUDA IPC (ranks of one
+    node, one process each).  Per decode step, :meth:`reduce_push` runs the reduce kernel with
+    its triples stored straight into every rank's buffer, and :meth:`merge` merges the rows from
+    the local buffer, waiting (bounded) for lines that have not arrived.  Data only ever moves
+    by stores into the consumer's memory; the step number is counted on the device, so both
+    launches take the same arguments every step and can be captured in a CUDA graph.
     """
 
     def __init__(self, num_rows: int, head_size: int, device: torch.device, group=None):
@@ -282,12 +284,11 @@ class PeerExchange:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.num_rows, self.head_size = num_rows, head_size
-        self.msg_floats = int(self._L.pa_packed_triple_floats(num_rows, head_size))
-        # one allocation of its own per rank (an inter-process handle names a whole allocation):
-        # recv [2][world][msg_floats] fp32, then the flag words [world] int32
-        self._flag_off = 4 * 2 * self.world * self.msg_floats
-        nbytes = self._flag_off + 4 * ((self.world + 3) // 4 * 4)
-        self.counters = torch.zeros(2, dtype=torch.int32, device=device)   # [1]: steps pushed, counted on the device
+        nbytes = int(self._L.pa_exchange_bytes(self.world, num_rows, head_size))
+        if nbytes <= 0:
+            raise ValueError("nothing to exchange (no rows, or an unsupported head size)")
+        self.counters = torch.zeros(2, dtype=torch.int32, device=device)   # [1]: steps merged, counted on the device
+        # an allocation of its own per rank: an inter-process handle names a whole allocation
         handle = C.create_string_buffer(_lib.PA_IPC_HANDLE_BYTES)
         own = C.c_void_p()
         with torch.cuda.device(device):
@@ -307,8 +308,7 @@ class PeerExchange:
             self._mapped.append(ptr.value)
             bases.append(ptr.value)
         self._recv_ptrs = (C.c_void_p * self.world)(*bases)
-        self._flag_ptrs = (C.c_void_p * self.world)(*[b + self._flag_off for b in bases])
-        dist.barrier(group)       # every rank has mapped every buffer before anybody pushes
+        dist.barrier(group)       # every rank has mapped every buffer before anybody stores
 
     def close(self) -> None:
         """Unmaps the peers' buffers, then (after every rank has done so) frees this rank's.
@@ -325,22 +325,20 @@ class PeerExchange:
             self._lib.check(self._L.pa_exchange_free(self._own), "pa_exchange_free")
         self._own = None
 
-    def push(self, message: torch.Tensor) -> None:
-        """Next step: stores ``message`` (packed triples, fp32) everywhere and raises the flags.
-        The step number is counted on the device, so push + merge can be captured in a CUDA graph."""
-        with torch.cuda.device(message.device):
+    def reduce_push(self, params) -> None:
+        """Next step: the reduce over this rank's partitions, its triples stored into every rank's buffer."""
+        with torch.cuda.device(self.device):
             stream = torch.cuda.current_stream().cuda_stream
-            self._lib.check(self._L.pa_push_message_sm100(message.data_ptr(), self.msg_floats, self._recv_ptrs,
-                                                          self._flag_ptrs, self.counters.data_ptr(), self.world, self.rank,
-                                                          0, stream), "pa_push_message_sm100")
+            self._lib.check(self._L.pa_reduce_push_sm100(C.byref(params), self._recv_ptrs, self.counters.data_ptr(),
+                                                         self.world, self.rank, 0, stream), "pa_reduce_push_sm100")
 
     def merge(self, out: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Waits for the current step's messages of all ranks and merges them into ``out`` (bf16)."""
+        """Merges the current step's triples of all ranks into ``out`` (bf16), waiting for late ones."""
         flat = out.view(-1, self.head_size)
         with torch.cuda.device(out.device):
             stream = torch.cuda.current_stream().cuda_stream
             self._lib.check(self._L.pa_merge_wait_sm100(flat.data_ptr(), flat.stride(0), self._own,
-                                                        self._own + self._flag_off, self.counters.data_ptr(),
+                                                        self.counters.data_ptr(),
                                                         status.data_ptr() if status is not None else None,
                                                         self.world, 0, self.num_rows, self.head_size, stream),
                             "pa_merge_wait_sm100")
@@ -403,13 +401,11 @@ class KvShardedDecoder:
             raise ValueError("exchange must be 'nccl' or 'p2p'")
         self.status = status
         self.peer = PeerExchange(R, D, dev, group) if (exchange == "p2p" and self.world > 1) else None
-        if self.peer is not None:
-            self.launches_per_step = 4
 
     def capture(self) -> "torch.cuda.CUDAGraph":
         """One step captured in a CUDA graph (collective: every rank calls it).  The launches of a
         step take the same arguments every time (the peer exchange counts its steps on the
-        device), and four short kernels per step are otherwise bound by the host's launch rate."""
+        device), and three short kernels per step are otherwise bound by the host's launch rate."""
         self.step()                       # anything lazy (communicator set-up) happens outside the capture
         torch.cuda.synchronize(self.query.device)
         graph = torch.cuda.CUDAGraph()
@@ -427,11 +423,11 @@ class KvShardedDecoder:
         with torch.cuda.device(self.query.device):
             stream = torch.cuda.current_stream().cuda_stream
             lib.check(L.pa_partition_sm100(C.byref(self.params), stream), "pa_partition_sm100")
+            if self.peer is not None:   # the reduce stores into every rank's buffer; merge what arrives here
+                self.peer.reduce_push(self.params)
+                return self.peer.merge(self.out, self.status)
             lib.check(L.pa_reduce_sm100(C.byref(self.params), base, base + 4 * R, base + 4 * self._o_off, stream),
                       "pa_reduce_sm100")
-            if self.peer is not None:   # push to every rank's buffer, wait for theirs, merge
-                self.peer.push(self.msg)
-                return self.peer.merge(self.out, self.status)
             gathered = self.msg
             if self.world > 1:      # one collective per step
                 dist.all_gather_into_tensor(self.msg_all, self.msg, group=self.group)
