@@ -342,7 +342,21 @@ int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
   auto kern = pa::tc::pa_partition_fp8_tc_kernel<BS, QR, PT, TRACE, ALIBI>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
   if (e != cudaSuccess) return cuda_fail(e);
-  kern<<<plan.grid, pa::tc::kThreads, plan.smem, stream>>>(plan.kp, plan.vmap);
+  // Programmatic dependent launch: in a decode loop the CTAs may become resident and set up their
+  // barriers and tensor memory while the kernel before this one in the stream (the previous step's
+  // reduce) drains; the kernel waits (griddepcontrol.wait) before it reads or writes global memory.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)plan.grid);
+  cfg.blockDim = dim3(pa::tc::kThreads);
+  cfg.dynamicSmemBytes = (size_t)plan.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kern, plan.kp, plan.vmap);
+  if (e != cudaSuccess) return cuda_fail(e);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return PA_OK;

@@ -416,6 +416,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   // (padding rows of the last row block see nothing)
   for (int r = tid; r < 64; r += kThreads) row_lim[r] = r < p.eqG ? (p.L - 1 - r / p.G) : 0x7fffffff;
   if (warp == kWarpMma) tmem_alloc(sbase + kOffTmemPtr, tmem_cols(QR));
+  // Everything above touches this CTA's shared and tensor memory only and may run while the
+  // kernel before this one in the stream drains; from here on global memory is read and written.
+  grid_dependency_wait();
   const int n_sp = build_partition_index(p, seq_off, seq_ctx, reinterpret_cast<int*>(smem + kOffScan));
   fence_before_sync();
   __syncthreads();

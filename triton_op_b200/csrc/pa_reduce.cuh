@@ -62,6 +62,9 @@ template <int WPR>
 __global__ void __launch_bounds__(WPR == 16 ? 512 : 128) pa_reduce_kernel(const __grid_constant__ ReduceParams p) {
   constexpr int kWarps = WPR == 16 ? 16 : 4;
   constexpr int kRowsPerCta = kWarps / WPR;
+  // the next kernel in the stream (the next step's partition kernel) may become resident now; it
+  // waits for this grid to finish before it touches global memory
+  grid_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int slice = warp % WPR;
