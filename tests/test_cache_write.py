@@ -105,6 +105,74 @@ def test_cuda_write_is_bit_exact(bs, mode):
         assert torch.equal(sc_d[0].cpu(), sc_ref[0]) and torch.equal(sc_d[1].cpu(), sc_ref[1])
 
 
+def _prefill_slots(nb, bs, chunks, g):
+    """Slots of token streams that walk pages the way a prefill chunk does: consecutive positions of a
+    sequence from a start offset inside its first page, pages taken from a shuffled pool."""
+    pool = torch.randperm(nb, generator=g).tolist()
+    slots = []
+    for start, n in chunks:
+        pages = [pool.pop() for _ in range((start + n + bs - 1) // bs)]
+        slots += [pages[(start + i) // bs] * bs + (start + i) % bs for i in range(n)]
+    return slots
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("bs,mode", [(16, "per_token"), (16, "per_tensor"), (64, "per_token"), (64, "per_token_trans"),
+                                     (1024, "unscaled"), (16, "per_token_unaligned")])
+def test_cuda_write_of_long_streams_is_bit_exact(bs, mode):
+    """Streams with full runs of 16 consecutive slots, which one warp writes whole: prefill-style
+    chunks with ragged ends, single scattered tokens between them, a skipped token and a slot outside
+    the pool.  Same bytes and scales as the oracle's token-wise write."""
+    from oracle import pa_oracle
+    from triton_op_b200 import _lib
+    from triton_op_b200.cache_write import write_kv_cache
+    dev = "cuda:0"
+    hkv, d = 8, 128
+    nb = 400 if bs == 16 else (100 if bs == 64 else 12)
+    g = torch.Generator().manual_seed(7 + bs)
+    chunks = [(5, 700), (0, 512), (15, 33), (9, 1500), (3, 1), (0, 16), (1, 15), (8, 1290)]
+    slots = _prefill_slots(nb, bs, chunks, g)
+    used = set(slots)
+    free = [s for s in range(nb * bs) if s not in used]
+    singles = [free[i] for i in torch.randperm(len(free), generator=g)[:60].tolist()]
+    slots = slots[:1200] + singles[:30] + slots[1200:] + singles[30:]
+    slots[40] = -1                                               # skipped token inside a run
+    slots.append(nb * bs + 3)                                    # outside the pool: reported, skipped
+    T = len(slots)
+    slots = torch.tensor(slots, dtype=torch.int64)
+    key = (torch.randn(T, hkv, d, generator=g) * 3).to(torch.bfloat16)
+    value = torch.randn(T, hkv, d, generator=g).to(torch.bfloat16)
+    key[100] = 0
+    trans = mode.endswith("trans")
+    kc = torch.full((nb, hkv, d // 16, bs, 16), 1.0).to(FP8)
+    vc = (torch.full((nb, hkv, bs // 16, d, 16), 1.0) if trans else torch.full((nb, hkv, d, bs), 1.0)).to(FP8)
+    if mode.startswith("per_token"):
+        scales = (torch.full((nb, hkv, bs, 1), -1.0), torch.full((nb, hkv, bs, 1), -1.0))
+    elif mode == "per_tensor":
+        scales = (torch.tensor(0.0371), torch.tensor(0.0093))
+    else:
+        scales = (None, None)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    sc_ref = tuple(None if s is None else s.clone() for s in scales)
+    pa_oracle.write_kv_cache(key[:-1], value[:-1], kc_ref, vc_ref, slots[:-1], *sc_ref)
+    kc_d, vc_d = kc.to(dev), vc.to(dev)
+    sc_d = tuple(None if s is None else s.to(dev) for s in scales)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    key_d = key.to(dev)
+    if mode.endswith("unaligned"):      # rows 8 bytes off a 16-byte boundary: no vector accesses, every token written alone
+        wide = torch.zeros(T, hkv, d + 8, dtype=torch.bfloat16, device=dev)
+        wide[:, :, 4:4 + d] = key_d
+        key_d = wide[:, :, 4:4 + d]
+        assert key_d.data_ptr() % 16 == 8
+    write_kv_cache(key_d, value.to(dev), kc_d, vc_d, slots.to(dev), *sc_d, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == _lib.PA_DEV_BAD_PAGE_ID
+    assert torch.equal(kc_d.cpu().view(torch.uint8), kc_ref.view(torch.uint8))
+    assert torch.equal(vc_d.cpu().view(torch.uint8), vc_ref.view(torch.uint8))
+    if mode.startswith("per_token"):
+        assert torch.equal(sc_d[0].cpu(), sc_ref[0]) and torch.equal(sc_d[1].cpu(), sc_ref[1])
+
+
 @pytest.mark.gpu
 def test_slot_outside_the_pool_is_reported_and_skipped():
     from triton_op_b200 import _lib

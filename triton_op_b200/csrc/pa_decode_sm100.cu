@@ -746,6 +746,8 @@ int pa_cache_write_sm100(const PaCacheWriteParams* p, void* stream) {
   k.kv_is_fp8 = fp8;
   k.quant_mode = p->kv_quant_mode;
   k.v_trans = v_trans;
+  k.vec_ok = aligned16(p->value_cache) && !(p->v_stride_block & 15) && !(p->v_stride_head & 15) &&
+             aligned16(p->key) && !(p->key_stride_token & 7) && !(p->key_stride_head & 7);
   k.key_stride_tok = p->key_stride_token;
   k.key_stride_head = p->key_stride_head;
   k.value_stride_tok = p->value_stride_token;
@@ -758,9 +760,14 @@ int pa_cache_write_sm100(const PaCacheWriteParams* p, void* stream) {
   k.ks_stride_head = p->kv_scale_stride_head;
   k.status = p->status;
   const int64_t pairs = (int64_t)p->num_tokens * p->num_kv_heads;
-  const int64_t blocks = (pairs + 3) / 4;
+  // e4m3 caches: a warp per window of 16 tokens and head; bf16 caches: a warp per token and head
+  const int64_t warps = fp8 ? ((int64_t)p->num_tokens + 15) / 16 * p->num_kv_heads : pairs;
+  const int64_t blocks = (warps + 3) / 4;
   if (blocks > 0x7fffffff) return PA_ERR_TOO_LARGE;
-  pa::pa_cache_write_kernel<<<(unsigned)blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(k);
+  if (fp8)
+    pa::pa_cache_write_fp8_kernel<<<(unsigned)blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(k);
+  else
+    pa::pa_cache_write_kernel<<<(unsigned)blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(k);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return PA_OK;

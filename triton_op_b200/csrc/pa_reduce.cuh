@@ -103,7 +103,8 @@ __global__ void __launch_bounds__(WPR == 16 ? 512 : 128) pa_reduce_kernel(const 
       m = p.max_logits[ws_base + (int64_t)pi * p.ws_stride_part];
       l = p.exp_sums[ws_base + (int64_t)pi * p.ws_stride_part];
     }
-    constexpr int kFlight = 16;
+    // rows in flight: a 16-warp row has one 32-partition chunk per warp, taken in one round trip
+    constexpr int kFlight = WPR == 16 ? 32 : 16;
     uint2 raw[kFlight];  // requested before the maximum is known
 #pragma unroll
     for (int j = 0; j < kFlight; ++j)
