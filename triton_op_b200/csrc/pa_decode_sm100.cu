@@ -706,8 +706,21 @@ int pa_merge_wait_sm100(void* out, int64_t out_stride_row, const void* recv, int
   k.world = world_size;
   k.step = step;
   k.num_rows = num_rows;
-  pa::pa_merge_wait_kernel<<<(unsigned)((num_rows + 3) / 4), 128, 0, static_cast<cudaStream_t>(stream)>>>(k);
-  cudaError_t e = cudaGetLastError();
+  // Programmatic dependent launch without a dependency wait in the kernel: every line it reads says
+  // by its flag whether it has arrived, so the warps may start polling while the reduce kernel that
+  // feeds them (all of whose CTAs are resident by then) still runs.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((num_rows + 3) / 4));
+  cfg.blockDim = dim3(128);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, pa::pa_merge_wait_kernel, k);
+  if (e != cudaSuccess) return cuda_fail(e);
+  e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e);
   return PA_OK;
 }
