@@ -43,7 +43,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one partition-kernel launch divided by the
 # algorithmic KV bytes of that launch, from the ncu capture summarised in
 # profiles/partition_kernel_tcgen05_llama8b.md (32-sequence case; traffic grows in proportion).
-NCU_TRAFFIC_PER_KV_BYTE = 1.026
+NCU_TRAFFIC_PER_KV_BYTE = 1.024
 
 
 def measured_peak():
