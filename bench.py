@@ -41,9 +41,10 @@ UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one partition-kernel launch divided by the
-# algorithmic KV bytes of that launch, from the ncu capture summarised in
-# profiles/partition_kernel_tcgen05_llama8b.md (32-sequence case; traffic grows in proportion).
-NCU_TRAFFIC_PER_KV_BYTE = 1.024
+# algorithmic KV bytes of that launch, per workload, from the ncu captures summarised under
+# profiles/ (captured on the workload itself or on fewer of its sequences; traffic grows in
+# proportion to the sequences).  Workloads without a capture report no traffic.
+NCU_TRAFFIC_PER_KV_BYTE = {"cfg2_llama8b": 1.024, "cfg3_llama70b_mtp": 1.07, "cfg4_longctx": 1.036}
 
 
 def measured_peak():
@@ -419,7 +420,8 @@ def run_ours(args, rank: int, world: int, local: int):
         "roofline": {"bound": "hbm", "kernel": "partition kernel (pa_partition_sm100)", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind + " (torch copy_, read+write)", "unit": "GB/s", "frac": achieved / peak,
                      "us_per_launch": us_partition, "algorithmic_bytes": kv_bytes,
-                     "traffic": (NCU_TRAFFIC_PER_KV_BYTE * kv_bytes) if NCU_TRAFFIC_PER_KV_BYTE else None},
+                     "traffic": (NCU_TRAFFIC_PER_KV_BYTE[args.workload] * kv_bytes)
+                                if args.workload in NCU_TRAFFIC_PER_KV_BYTE else None},
         "cpu_baseline": cpu_baseline,
         "value_launch": "CUDA graph replay of the sharded step" if step_graph is not None else "eager launches",
         "e2e": {"value": total_kv / (ms_e2e * 1e-3) / 1e9, "unit": UNIT, "us_per_call": ms_e2e * 1e3,
