@@ -67,7 +67,7 @@ def _rank_main(rank: int, world: int, port: int, ret):
             ret["timeout_status"] = int(st2.item())
         dist.barrier()
         ex.close()
-        dec.peer.close()
+        dec.close()
     finally:
         dist.destroy_process_group()
 

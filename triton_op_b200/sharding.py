@@ -402,6 +402,12 @@ class KvShardedDecoder:
         self.status = status
         self.peer = PeerExchange(R, D, dev, group) if (exchange == "p2p" and self.world > 1) else None
 
+    def close(self) -> None:
+        """Releases the peer exchange's mapped buffers (collective; a no-op for the NCCL exchange)."""
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None
+
     def capture(self) -> "torch.cuda.CUDAGraph":
         """One step captured in a CUDA graph (collective: every rank calls it).  The launches of a
         step take the same arguments every time (the peer exchange counts its steps on the
