@@ -1154,6 +1154,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     // one call site each for softmax and epilogue: the code of this loop should stay small
     for (int i = grp; !dead; i += NG) {
       const bool more = i < n_local;
+      if (wq == 0) stamp(4, i, 3);
       if (more) {
         float sc_use[4];
 #pragma unroll
