@@ -91,31 +91,37 @@ __device__ __forceinline__ Item decode_item(int k, const KernelParams& p, const 
 // Builds, cooperatively over the CTA, seq_off[0..S] (exclusive prefix sum of the number of
 // partitions per sequence) and seq_ctx[0..S) (context lengths clamped to what the block table
 // can address).  Returns the total number of (sequence, partition) pairs.
-__device__ __forceinline__ int build_partition_index(const KernelParams& p, int* seq_off,
-                                                     int* seq_ctx, int* scan_scratch) {
+// (Run once per CTA: its loops stay rolled and it is not inlined, so that a cold start fetches a
+// few hundred bytes of it instead of ten kilobytes of unrolled divisions.)
+__device__ __noinline__ int build_partition_index(const KernelParams& p, int* seq_off,
+                                                  int* seq_ctx, int* scan_scratch) {
   const int tid = threadIdx.x, nthr = blockDim.x;
-  const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
+  const int lane = tid & 31, warp = tid >> 5;
   if (tid == 0) seq_off[0] = 0;
+  bool too_long = false;
+#pragma unroll 1
   for (int i = tid; i < p.S; i += nthr) {
     int c = p.context_lens[i];
     if (c > p.ctx_cap) {
       c = p.ctx_cap;
-      if (p.status) atomicOr(p.status, PA_DEV_CTX_TOO_LONG);
+      too_long = true;
     }
     if (c < 0) c = 0;
-    seq_ctx[i] = c;
     int np = (c + p.partition_size - 1) / p.partition_size;
     if (np > p.max_partitions) {  // workspace extent is the hard limit
       np = p.max_partitions;
-      seq_ctx[i] = np * p.partition_size;
-      if (p.status) atomicOr(p.status, PA_DEV_CTX_TOO_LONG);
+      c = np * p.partition_size;
+      too_long = true;
     }
+    seq_ctx[i] = c;
     seq_off[i + 1] = np;
   }
+  if (too_long && p.status) atomicOr(p.status, PA_DEV_CTX_TOO_LONG);
   __syncthreads();
   const int chunk = (p.S + nthr - 1) / nthr;
   const int beg = min(tid * chunk, p.S), end = min(beg + chunk, p.S);
   int sum = 0;
+#pragma unroll 1
   for (int i = beg; i < end; ++i) sum += seq_off[i + 1];
   int incl = sum;
 #pragma unroll
@@ -126,8 +132,9 @@ __device__ __forceinline__ int build_partition_index(const KernelParams& p, int*
   if (lane == 31) scan_scratch[warp] = incl;
   __syncthreads();
   int run = incl - sum;
+#pragma unroll 1
   for (int w = 0; w < warp; ++w) run += scan_scratch[w];
-  (void)nwarps;
+#pragma unroll 1
   for (int i = beg; i < end; ++i) {
     run += seq_off[i + 1];
     seq_off[i + 1] = run;
