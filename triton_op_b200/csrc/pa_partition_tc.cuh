@@ -374,6 +374,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   constexpr int kPStep = p_step_bytes(QR);
   constexpr int kPagesPerItem = BS >= kItemTokens ? 1 : kItemTokens / BS;
   extern __shared__ __align__(1024) uint8_t smem[];
+  const long long t_entry = TRACE ? clock64() : 0;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
@@ -419,6 +420,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   // Everything above touches this CTA's shared and tensor memory only and may run while the
   // kernel before this one in the stream drains; from here on global memory is read and written.
   grid_dependency_wait();
+  const long long t_dep = TRACE ? clock64() : 0;
   const int n_sp = build_partition_index(p, seq_off, seq_ctx, reinterpret_cast<int*>(smem + kOffScan));
   fence_before_sync();
   __syncthreads();
@@ -442,6 +444,11 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     if (TRACE && p.trace != nullptr && blockIdx.x == 0 && lane == 0 && item < 64)
       p.trace[(role * 64 + item) * 4 + point] = (unsigned long long)clock64();
   };
+  if (TRACE && p.trace != nullptr && blockIdx.x == 0 && tid == 0) {   // entry, dependency wait passed, set-up done
+    p.trace[(7 * 64 + 60) * 4 + 0] = (unsigned long long)t_entry;
+    p.trace[(7 * 64 + 60) * 4 + 1] = (unsigned long long)t_dep;
+    p.trace[(7 * 64 + 60) * 4 + 2] = (unsigned long long)clock64();
+  }
   auto fail = [&]() {
     dead = true;
     if (lane == 0) report_status(p.status, PA_DEV_WAIT_TIMEOUT);
@@ -1180,6 +1187,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   __syncwarp();
   fence_before_sync();
   __syncthreads();
+  if (TRACE && p.trace != nullptr && blockIdx.x == 0 && tid == 0)
+    p.trace[(7 * 64 + 60) * 4 + 3] = (unsigned long long)clock64();
   if (warp == kWarpMma) {
     fence_after_sync();
     tmem_dealloc(tmem_base, tmem_cols(QR));
