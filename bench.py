@@ -295,9 +295,16 @@ def run_ours(args, rank: int, world: int, local: int):
     flush_l2 = kv_bytes < 2 * L2_BYTES
     flush_buf = torch.empty(64 << 20, dtype=torch.int32, device=dev) if flush_l2 else None
 
+    align = torch.zeros(1, dtype=torch.float32, device=dev) if (flush_l2 and world > 1) else None
+
     def flush():
         flush_buf.zero_()
         flush_buf.sum()
+        if align is not None:
+            # the ranks' flushes do not end together; without this the first rank's step would be
+            # timed waiting for the last rank's flush.  (One element: it leaves L2 as the flush did.)
+            import torch.distributed as dist
+            dist.all_reduce(align)
 
     def timed_steps(fn, n):
         """Milliseconds per call of fn over n calls, on the device."""
