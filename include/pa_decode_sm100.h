@@ -100,7 +100,9 @@ typedef struct PaDecodeParams {
   void* tmp_out;               /* [S, Hkv, P, eqG, D] out_dtype, already divided by exp_sums */
   int32_t* status;             /* optional device int32, OR-ed with PA_DEV_* bits */
   uint64_t* trace;             /* optional tuning aid: device buffer of PA_TRACE_WORDS uint64 that
-                                * receives SM-clock stamps of CTA 0's pipeline roles; NULL normally */
+                                * receives SM-clock stamps of CTA 0's pipeline roles; NULL normally.
+                                * Only a library built with -DPA_TRACE_BUILD writes it (16-token pages);
+                                * the default build ignores it. */
 
   /* sizes */
   int32_t num_seqs;            /* S */

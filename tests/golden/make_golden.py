@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz from the reference checkout (run where it is mounted):
 
-    python tests/golden/make_golden.py [/path/to/yanguahe_triton_op]
+    python tests/golden/make_golden.py /path/to/yanguahe_triton_op
 
 The two functions of the reference's pure-PyTorch path (``reference_masked_attention`` and
 ``torch_mha_extend``, test_pa_mtp.py:175-291) are extracted from the file by their AST nodes
@@ -66,7 +66,9 @@ def input_digest(inp) -> Dict[str, str]:
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a yanguahe/triton_op checkout>")
+    ref_root = sys.argv[1]
     torch_mha_extend = load_reference_functions(ref_root)
     torch.set_num_threads(1)  # reduction order of the CPU kernels must not depend on the host
     for name, (cfg, seed, dist) in CASES.items():

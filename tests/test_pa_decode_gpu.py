@@ -165,6 +165,33 @@ def test_tuning_knobs_do_not_change_results():
         assert_close(out, ref, what=str(tune))
 
 
+def test_ring_depths_never_drop_below_the_issue_lag():
+    """The host plan keeps the K ring of the tcgen05 kernel at least as deep as the three softmax
+    groups and the V ring at least two deep; a request for less, or a batch whose in-kernel index
+    leaves no room for that, is refused instead of launching a shallower ring (nothing is launched
+    here: the plan is queried)."""
+    from triton_op_b200 import _lib
+    from triton_op_b200.inputs import DecodeConfig, make_inputs
+    from triton_op_b200.pa_decode import query_launch
+    inp = golden_inputs("gqa4_ragged").to(DEV)
+    c = inp.cfg
+    args = lambda i: (torch.empty_like(i.query), i.query, i.key_cache, i.value_cache, i.context_lens, i.block_tables,
+                      i.softmax_scale, i.cfg.query_len, i.max_context, torch.bfloat16, None, i.key_scale, i.value_scale)
+    assert query_launch(*args(inp))["ring_stages"] >= 3
+    assert query_launch(*args(inp), tune={"stages": 3})["ring_stages"] == 3
+    for tune in ({"stages": 2}, {"stages": 1}, {"vstages": 1}):
+        with pytest.raises(_lib.PaError) as err:
+            query_launch(*args(inp), tune=tune)
+        assert err.value.status == -3, tune
+    # thousands of sequences: the index eats into the rings, which shrink to (3, 2) and no further
+    big = make_inputs(DecodeConfig("many", 4000, 4, 1, 16, 1, ("fixed", 16)), seed=5, device=DEV)
+    assert query_launch(*args(big))["ring_stages"] >= 3
+    huge = make_inputs(DecodeConfig("too_many", 12000, 4, 1, 16, 1, ("fixed", 16)), seed=5, device=DEV)
+    with pytest.raises(_lib.PaError) as err:
+        query_launch(*args(huge))
+    assert err.value.status == -7
+
+
 def test_zero_length_sequences_and_empty_batch():
     from triton_op_b200.inputs import DecodeConfig, make_inputs
     cfg = DecodeConfig("zeros", 5, 8, 2, 16, 1, ("fixed", 100))

@@ -47,11 +47,14 @@ def test_noalloc_entry_point_matches_the_normal_one_twice_in_a_row():
             q.exp_sums = None            # ignored by the variant: it brings its own workspaces
             q.max_logits = None
             q.tmp_out = None
+            torch.cuda.synchronize()
             mem_before = torch.cuda.memory_allocated(DEV)
+            free_before = torch.cuda.mem_get_info(DEV)[0]      # the driver's view: sees a cudaMalloc torch would not
             rc = lib.pa_decode_noalloc_sm100(C.byref(q), stream)
             assert rc == 0, lib.pa_strerror(rc)
             torch.cuda.synchronize()
             assert torch.cuda.memory_allocated(DEV) == mem_before
+            assert torch.cuda.mem_get_info(DEV)[0] >= free_before
             assert not torch.isnan(got).any()
             # same kernels on the same inputs: equal well inside the tolerance of the other tests
             assert_close(got, want, what=f"{name}: noalloc vs normal entry point")
@@ -71,3 +74,10 @@ def test_noalloc_entry_point_refuses_what_does_not_fit():
         rc = lib.pa_decode_noalloc_sm100(C.byref(p), torch.cuda.current_stream().cuda_stream)
     assert rc == -7 and b"limit" in lib.pa_strerror(rc)
     assert lib.pa_decode_noalloc_sm100(None, None) == -1
+    # sizes whose product wraps around 64 bits must not slip under the limit
+    p, keep = _params(inp, out)
+    p.num_kv_heads = 2 ** 31 - 1
+    p.max_partitions = 2 ** 31 - 1
+    p.num_seqs = 2 ** 31 - 1
+    with torch.cuda.device(DEV):
+        assert lib.pa_decode_noalloc_sm100(C.byref(p), torch.cuda.current_stream().cuda_stream) == -7

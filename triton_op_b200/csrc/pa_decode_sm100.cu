@@ -262,11 +262,16 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
     off = round_up(off + index_bytes, 128);
     k.off_q = off;
     const int qslot = pa::tc::q_slot_bytes(qr, per_token);
-    // ring depths (K and query ring, V ring), deepest that fits
-    static const int kDepths[][2] = {{4, 4}, {4, 3}, {3, 3}, {3, 2}, {2, 2}, {2, 1}};
+    // Ring depths (K ring, V ring), deepest that fits.  The K ring is never shallower than the
+    // three softmax groups (P.V trails QK^T by two items in the issue loop, and a group's waits
+    // on the ring barriers assume a slot is not refilled within that lag), the V ring never
+    // shallower than two; a batch whose in-kernel index leaves no room for that is refused.
+    static const int kDepths[][2] = {{4, 4}, {4, 3}, {3, 3}, {3, 2}};
+    if (p->tune_stages > 0 && p->tune_stages < 3) return PA_ERR_UNSUPPORTED;
+    if (p->tune_vstages > 0 && p->tune_vstages < 2) return PA_ERR_UNSUPPORTED;
     bool placed = false;
     for (const auto& d : kDepths) {
-      if (p->tune_stages > 0 && d[0] > p->tune_stages && d[0] > 2) continue;
+      if (p->tune_stages > 0 && d[0] > p->tune_stages) continue;
       if (p->tune_vstages > 0 && d[1] != p->tune_vstages) continue;
       const int off_p = round_up(off + pa::tc::kQSlots * qslot, 128);
       const int ring = round_up(off_p + pa::tc::kNG * pa::tc::p_tile_bytes(qr), 1024);
@@ -385,8 +390,11 @@ int launch_partition(const LaunchPlan& plan, cudaStream_t stream) {
   if (plan.kp.S == 0) return PA_OK;
   if (plan.tensor_path) {
     switch (plan.kp.block_size) {
-      case 16:  // the tuning build (clock stamps compiled in) exists for this page size only
-        return plan.kp.trace != nullptr ? launch_tensor_bs<16, true>(plan, stream) : launch_tensor_bs<16, false>(plan, stream);
+      case 16:
+#ifdef PA_TRACE_BUILD   // tuning builds (-DPA_TRACE_BUILD): clock stamps compiled in, this page size only
+        if (plan.kp.trace != nullptr) return launch_tensor_bs<16, true>(plan, stream);
+#endif
+        return launch_tensor_bs<16, false>(plan, stream);
       case 64: return launch_tensor_bs<64, false>(plan, stream);
       case 1024: return launch_tensor_bs<1024, false>(plan, stream);
       default: return PA_ERR_UNSUPPORTED;
@@ -550,8 +558,17 @@ int pa_decode_noalloc_sm100(const PaDecodeParams* params, void* stream) {
   if (params->num_seqs < 0 || params->num_kv_heads <= 0 || params->query_group_size <= 0 ||
       params->query_len <= 0 || params->max_partitions <= 0 || params->head_size != pa::kD)
     return PA_ERR_BAD_SHAPE;
+  // rows = S * Hkv * P * eqG, built up factor by factor against the array's capacity so that no
+  // product of caller-supplied sizes can overflow (and wrap back under the limit)
+  if (params->query_len > 4 || params->query_group_size > 64) return PA_ERR_UNSUPPORTED;
   const int64_t eqG = (int64_t)params->query_group_size * params->query_len;
-  const int64_t rows = (int64_t)params->num_seqs * params->num_kv_heads * params->max_partitions * eqG;
+  const int64_t max_rows = (int64_t)PA_NOALLOC_SCRATCH_BYTES / (8 + pa::kD * 2);
+  int64_t rows = eqG;
+  const int64_t factors[3] = {params->num_seqs, params->num_kv_heads, params->max_partitions};
+  for (const int64_t f : factors) {
+    if (f > 0 && rows > max_rows / f) return PA_ERR_TOO_LARGE;
+    rows *= f;
+  }
   const int64_t f32_bytes = (rows * 4 + 255) / 256 * 256;       // exp_sums, then max_logits
   const int64_t need = 2 * f32_bytes + rows * pa::kD * 2;       // then tmp_out (bf16)
   if (need > (int64_t)PA_NOALLOC_SCRATCH_BYTES) return PA_ERR_TOO_LARGE;

@@ -26,8 +26,12 @@
 //    item are prefetched one item ahead so the dependent block-table load never stalls.
 //    Because a ring is private to one warp there is no inter-warp synchronisation at all in
 //    the steady state; the only waits are on the warp's own copies (bounded).
-//  * Math runs on the e4m3 tensor-core tile m16n8k32 straight from the fp8 bytes in shared
-//    memory (no dequantisation pass, no fp8->f16 converts).  The query (bf16) is split into
+//  * Math is written as the e4m3 tile mma.sync.m16n8k32 on the fp8 bytes in shared memory, with
+//    no dequantisation pass in the source.  sm_100a has no native e4m3 mma.sync, though: the
+//    compiler expands each tile into byte->half converts plus f16 tiles, and that convert pipe
+//    is what bounds this kernel near 4.2 TB/s (the tcgen05 kernel in pa_partition_tc.cuh, which
+//    feeds e4m3 operands to the tensor core from shared memory, serves the 256-token partition
+//    size for that reason; this kernel covers the other partition sizes).  The query (bf16) is split into
 //    hi + lo/16, two e4m3 numbers per element, exactly (8 significant bits); hi rows live in
 //    tile rows 0-7 and lo rows in rows 8-15, so one M=16 tile serves 8 query rows at bf16
 //    precision.  The probabilities get the same hi/lo treatment for P.V.  Products are exact

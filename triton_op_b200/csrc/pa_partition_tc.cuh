@@ -457,7 +457,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   auto wait = [&](uint32_t b, uint32_t parity) -> bool {
     return __all_sync(kFullMask, mbar_wait(b, parity));
   };
-  // block-table entry of page `pg` (counted inside the item) of an item, clamped
   // Block-table entry of page `pg` (counted inside the item) of an item, as loaded: the roles
   // fetch it an item ahead and must not touch the value before they use it (a comparison right
   // after the load would make them wait for it there), so clamping is a separate step.

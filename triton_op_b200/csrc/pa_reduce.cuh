@@ -14,22 +14,26 @@
 
 namespace pa {
 
-// Triples that cross GPUs travel as flagged 16-byte lines {value, step, value, step}: each
-// 8-byte half is written and read as a unit, so a reader that finds the step number it waits
-// for in both halves has the values too -- no fence, no separate flag, one trip over the link.
-// A row's triple is 1 + kD / 2 lines: {m, l}, then {o[2i], o[2i+1]}.
+// Triples that cross GPUs travel as flagged 16-byte lines {value, step, value, step}.  Each
+// {value, step} pair is ONE naturally aligned 64-bit element of a two-element vector access: the
+// memory model makes no promise about the order in which the elements of a vector access become
+// visible, but every element is written and read whole, so a reader that finds the step number it
+// waits for in a half has that half's value too -- no fence, no separate flag, one trip over the
+// link.  A row's triple is 1 + kD / 2 lines: {m, l}, then {o[2i], o[2i+1]}.
 constexpr int kMaxPeers = 16;
 constexpr int kLinesPerRow = 1 + kD / 2;
 
 __device__ __forceinline__ void st_line(uint4* dst, float a, float b, int step) {
-  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(__float_as_uint(a)), "r"(step),
-               "r"(__float_as_uint(b)), "r"(step)
+  const uint64_t hi = (uint64_t)(uint32_t)step << 32;
+  asm volatile("st.volatile.global.v2.b64 [%0], {%1, %2};" ::"l"(dst), "l"(hi | __float_as_uint(a)),
+               "l"(hi | __float_as_uint(b))
                : "memory");
 }
+// Returns the line as {value a, step of a, value b, step of b}.
 __device__ __forceinline__ uint4 ld_line(const uint4* src) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
-  return v;
+  uint64_t a, b;
+  asm volatile("ld.volatile.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(src) : "memory");
+  return make_uint4((uint32_t)a, (uint32_t)(a >> 32), (uint32_t)b, (uint32_t)(b >> 32));
 }
 
 struct ReduceParams {

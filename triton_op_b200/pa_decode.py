@@ -167,7 +167,9 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
         hit = _PARAM_CACHE.get(key) if key is not None else None
         if hit is not None:
             p, ws = hit
-            return p, (output, query, key_cache, value_cache, sequence_lengths, block_tables, query_scale,
+            # a private copy: callers keep and edit their block (tuning sweeps, the no-allocation
+            # entry point's tests), and the cached one must stay as validated
+            return PaDecodeParams.from_buffer_copy(p), (output, query, key_cache, value_cache, sequence_lengths, block_tables, query_scale,
                        key_scale, value_scale, alibi_slopes) + ws + (status,)
     p, keep, cacheable = _build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
                                        softmax_scale, query_sequence_length, max_sequence_length, compute_type,
@@ -176,7 +178,7 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
     if key is not None and cacheable:
         if len(_PARAM_CACHE) >= 16:
             _PARAM_CACHE.clear()
-        _PARAM_CACHE[key] = (p, keep[10:13])    # the block and the workspaces it points into
+        _PARAM_CACHE[key] = (PaDecodeParams.from_buffer_copy(p), keep[10:13])    # the block and the workspaces it points into
     return p, keep
 
 
