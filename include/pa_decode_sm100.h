@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define PA_ABI_VERSION 2
+#define PA_ABI_VERSION 3
 
 typedef enum PaStatus {
   PA_OK = 0,
@@ -103,6 +103,17 @@ typedef struct PaDecodeParams {
                                 * receives SM-clock stamps of CTA 0's pipeline roles; NULL normally.
                                 * Only a library built with -DPA_TRACE_BUILD writes it (16-token pages);
                                 * the default build ignores it. */
+  int32_t* merge_counters;     /* optional [S*Hkv] device int32, ZERO before the first call and left zero by
+                                * every call that completes.  With it and tune_fuse = 1, pa_decode_sm100 runs as
+                                * ONE launch where it can (e4m3fn KV, partition 256, L*G <= 8, P <= 32, no
+                                * ALiBi): four extra warps of the partition kernel count the stored partitions
+                                * of every (sequence, kv head) here and merge a row set once its last
+                                * partition is in, instead of a second launch (the reference always pays that
+                                * launch, pa_decode_triton_gluon_fp8.py:1862-1887).  Same bits as the two-launch
+                                * form.  It is not the default: the end of the single launch (a GPU-scope
+                                * fence on each side of the counter before the last rows can be merged) takes
+                                * longer than the separate reduce kernel does.  One array serves one call at a
+                                * time; after a call that reported PA_DEV_WAIT_TIMEOUT clear it again. */
 
   /* sizes */
   int32_t num_seqs;            /* S */
@@ -140,9 +151,13 @@ typedef struct PaDecodeParams {
    * warp (K ring of the tcgen05 kernel); tune_vstages: V ring depth of the tcgen05 kernel;
    * tune_ctas: grid size.  For benchmarking sweeps; results do not depend on them. */
   int32_t tune_warps, tune_stages, tune_ctas, tune_vstages;
+  int32_t tune_fuse;           /* 1: run pa_decode_sm100 as ONE launch where merge_counters and the shape allow it;
+                                * 0 (default): partition kernel, then reduce kernel (measured faster, see the field) */
+  int32_t reserved0;
 } PaDecodeParams;
 
-/* Partition kernel followed by the reduce kernel on `stream` (a cudaStream_t). */
+/* Partition kernel followed by the reduce kernel on `stream` (a cudaStream_t); one launch that
+ * does both when `merge_counters` is given and the shape allows it (see the field). */
 int pa_decode_sm100(const PaDecodeParams* params, void* stream);
 
 /* The partition kernel alone: fills exp_sums / max_logits / tmp_out, leaves `out` untouched. */
@@ -299,6 +314,15 @@ int pa_query_launch_sm100(const PaDecodeParams* params, int32_t* grid_ctas, int3
  */
 #define PA_NOALLOC_SCRATCH_BYTES (16u << 20)
 int pa_decode_noalloc_sm100(const PaDecodeParams* params, void* stream);
+
+/*
+ * Measurement aid (no counterpart in the reference): reads `bytes_each` bytes (a multiple of
+ * 8192) from each of the two device regions `a` and `b` with the partition kernels' own copy
+ * mechanism (2 KB bulk copies into shared-memory rings, one persistent CTA per SM) and computes
+ * nothing.  Its duration is the read-only streaming ceiling the benchmark quotes the decode
+ * call against.  `status` (optional) receives PA_DEV_WAIT_TIMEOUT if a bounded wait ran out.
+ */
+int pa_stream_probe_sm100(const void* a, const void* b, int64_t bytes_each, int32_t* status, void* stream);
 
 /* Static string for a PaStatus. */
 const char* pa_strerror(int status);

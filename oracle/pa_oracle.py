@@ -19,9 +19,12 @@ reference:
 Parity pin: ``tests/golden/*.npz`` hold outputs of the reference's own two functions, loaded
 from the reference checkout by ``tests/golden/make_golden.py`` and run on CPU; the CPU test
 suite checks this module against them bit for bit (same torch ops in the same order), so the
-oracle is pinned to the reference, not merely to itself.  The split-KV intermediates have no
-golden in the reference (its kernels only run on AMD GPUs); ``merge_partials(split_kv_partials)``
-is pinned against ``paged_attention`` instead.
+oracle is pinned to the reference, not merely to itself.  The ALiBi bias and the split-KV
+intermediates, which that PyTorch path does not have, are pinned by ``tests/golden/triton_*.npz``:
+outputs of the reference's plain-Triton decode (pa_decode_triton.py:523-685) run on CPU under the
+Triton interpreter by ``tests/golden/make_golden_triton.py`` (fp16 arithmetic there, so the
+comparison has an fp16-level tolerance, stated in the test).  Sink tokens exist only in a Gluon
+reduce kernel the reference never launches: parity of ``sink_tokens`` is unpinned by the reference.
 """
 from __future__ import annotations
 
@@ -130,7 +133,8 @@ def split_kv_partials(query: torch.Tensor, key_cache: torch.Tensor, value_cache:
                       block_tables: torch.Tensor, context_lens: torch.Tensor, query_len: int,
                       softmax_scale: float, partition_size: int,
                       key_scale: Optional[torch.Tensor] = None,
-                      value_scale: Optional[torch.Tensor] = None
+                      value_scale: Optional[torch.Tensor] = None,
+                      alibi_slopes: Optional[torch.Tensor] = None
                       ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Exact-fp32 statement of the partition kernel's outputs.
 
@@ -140,7 +144,9 @@ def split_kv_partials(query: torch.Tensor, key_cache: torch.Tensor, value_cache:
     m = max_j s_j, l = sum_j exp(s_j - m), o = sum_j exp(s_j - m) v_j / l over the partition's
     visible keys (pa_decode_triton_gluon_fp8.py:929-937,979-1002).  Row (t, g) sees key j iff
     ``(L-1-t) + j < ctx`` (:915-920).  Partitions with no visible key hold m=-inf, l=0, o=0;
-    partitions beyond the context are left at m=-inf, l=0, o=0 as well.
+    partitions beyond the context are left at m=-inf, l=0, o=0 as well.  ``alibi_slopes``
+    ``[Hkv*G]``: the bias ``slope[head] * (j - (ctx - 1))`` on the scaled scores
+    (pa_decode_triton.py:148-151, pa_decode_triton_gluon_fp8.py:905-908).
     """
     nb, hkv, d, bs = value_cache.shape
     S = query.shape[0]
@@ -159,6 +165,10 @@ def split_kv_partials(query: torch.Tensor, key_cache: torch.Tensor, value_cache:
         keys, values = gather_sequence(k_flat, v_flat, block_tables[s], ctx, bs, key_scale, value_scale)
         q = query[s].float().view(hkv, eqg, d)                       # [Hkv, eqG, D]
         scores = torch.einsum("hrd,khd->hrk", q, keys) * softmax_scale   # [Hkv, eqG, ctx]
+        if alibi_slopes is not None:
+            rel = torch.arange(ctx, dtype=torch.float32) - (ctx - 1)
+            slope_of_row = alibi_slopes.float().view(hkv, G)[:, torch.arange(eqg) % G]      # [Hkv, eqG]
+            scores = scores + slope_of_row[..., None] * rel
         t_of_row = torch.arange(eqg) // G
         limit = ctx - (query_len - 1 - t_of_row)                      # [eqG]
         visible = torch.arange(ctx)[None, :] < limit[:, None]        # [eqG, ctx]

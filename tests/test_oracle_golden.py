@@ -65,3 +65,56 @@ def test_compare_arrays_metrics():
     assert sum(s["count"] for s in r["threshold_stats"]) == 4
     with pytest.raises(ValueError):
         pa_oracle.compare_arrays(a, b[:1])
+
+
+# ----------------------------------------------------------------------------- fixtures run by the reference's Triton path
+import importlib.util as _ilu
+import os as _os
+
+import numpy as _np
+
+_spec = _ilu.spec_from_file_location("make_golden_triton", _os.path.join(_os.path.dirname(__file__), "golden", "make_golden_triton.py"))
+make_golden_triton = _ilu.module_from_spec(_spec)
+_spec.loader.exec_module(make_golden_triton)
+
+
+def load_triton_golden(name):
+    z = _np.load(_os.path.join(_os.path.dirname(__file__), "golden", name + ".npz"))
+    g = {k: torch.from_numpy(z[k].copy()) for k in ("out", "tmp_output", "exp_sums", "max_logits", "alibi_slopes", "context_lens")}
+    g["digest"] = dict(zip(z["digest_keys"].tolist(), z["digest_vals"].tolist()))
+    return g
+
+
+# The reference computed these in fp16 (scaled query, probabilities, partial and final outputs all
+# rounded to fp16, fp32 accumulation); the oracle is fp32 throughout.  Tolerances are fp16-level.
+TRITON_OUT_TOL = dict(atol=3e-3, rtol=1e-2)
+TRITON_LOGIT_TOL = dict(atol=1e-2, rtol=2e-3)
+TRITON_SUM_TOL = dict(atol=1e-3, rtol=1e-2)
+
+
+@pytest.mark.parametrize("name", sorted(make_golden_triton.CASES))
+def test_oracle_alibi_and_split_kv_match_the_reference_triton_run(name):
+    """Outputs and split-KV intermediates of pa_decode_triton.paged_attention_decode (run on CPU under
+    the Triton interpreter, with and without alibi_slopes) against the oracle: pins the oracle's ALiBi
+    bias (slope * (key position - (context - 1)), per query head) and its (max, sum, normalised
+    output) statement per 256-token partition to something the reference itself executed."""
+    gold = load_triton_golden(name)
+    inp, slopes = make_golden_triton.case_inputs(name)
+    assert make_golden.input_digest(inp) == gold["digest"], "seeded inputs differ from the fixture's"
+    c = inp.cfg
+    if slopes is not None:
+        assert torch.equal(slopes, gold["alibi_slopes"])
+    out = pa_oracle.paged_attention(inp.query_tokens, inp.key_cache, inp.value_cache, inp.block_tables, inp.context_lens,
+                                    inp.query_indptr(), None, None, alibi_slopes=slopes).float()
+    assert torch.allclose(out, gold["out"], **TRITON_OUT_TOL), float((out - gold["out"]).abs().max())
+    m, l, o = pa_oracle.split_kv_partials(inp.query, inp.key_cache, inp.value_cache, inp.block_tables, inp.context_lens,
+                                          1, inp.softmax_scale, 256, None, None, alibi_slopes=slopes)
+    for s in range(c.num_seqs):
+        np_s = (int(inp.context_lens[s]) + 255) // 256
+        assert torch.allclose(m[s, :, :np_s], gold["max_logits"][s, :, :np_s], **TRITON_LOGIT_TOL)
+        assert torch.allclose(l[s, :, :np_s], gold["exp_sums"][s, :, :np_s], **TRITON_SUM_TOL)
+        assert torch.allclose(o[s, :, :np_s], gold["tmp_output"][s, :, :np_s], **TRITON_OUT_TOL)
+    if slopes is not None:      # the bias matters on these cases: without it the oracle is far off
+        plain = pa_oracle.paged_attention(inp.query_tokens, inp.key_cache, inp.value_cache, inp.block_tables,
+                                          inp.context_lens, inp.query_indptr(), None, None).float()
+        assert (plain - gold["out"]).abs().max() > 0.1

@@ -192,6 +192,42 @@ def test_ring_depths_never_drop_below_the_issue_lag():
     assert err.value.status == -7
 
 
+@pytest.mark.parametrize("name", ["cfg1_small", "gqa4_ragged", "mtp2_g8", "mtp4_g2_pertoken", "pertoken_g8", "bs64_g5"])
+def test_single_launch_decode_matches_the_two_launch_form(name):
+    """tune fuse = 1: the decode call is one launch (four extra warps of the partition kernel merge a
+    row set when its last partition is stored).  Same arithmetic in the same order as the reduce
+    kernel: bit-identical outputs, counters back at zero, twice in a row."""
+    from triton_op_b200.pa_decode import get_merge_counters, query_launch
+    inp = golden_inputs(name).to(DEV)
+    c = inp.cfg
+    two, res2 = run_operator(inp)
+    launch = query_launch(torch.empty_like(inp.query), inp.query, inp.key_cache, inp.value_cache, inp.context_lens,
+                          inp.block_tables, inp.softmax_scale, c.query_len, inp.max_context, torch.bfloat16, None,
+                          inp.key_scale, inp.value_scale, tune={"fuse": 1})
+    assert launch["cta_threads"] == (20 if c.q_heads // c.kv_heads * c.query_len <= 8 else 16) * 32   # the single-launch kernel has four merge warps
+    for _ in range(2):
+        st = _status()
+        one, res1 = run_operator(inp, status=st, tune={"fuse": 1})
+        torch.cuda.synchronize()
+        assert int(st.item()) == 0
+        assert torch.equal(one.view(torch.int16), two.view(torch.int16))
+        counters = get_merge_counters(res1["temporary_output"], c.num_seqs, c.kv_heads)
+        assert int(counters.abs().sum().item()) == 0
+    assert_close(one, load_golden(name)["out"], what=f"{name}: single launch")
+
+
+def test_single_launch_decode_on_the_benchmark_shape():
+    from triton_op_b200.inputs import CONFIGS, make_inputs
+    inp = make_inputs(CONFIGS["cfg2_llama8b"], seed=3, device=DEV, num_seqs=24)
+    two, _ = run_operator(inp)
+    st = _status()
+    for _ in range(3):
+        one, _ = run_operator(inp, status=st, tune={"fuse": 1})
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert torch.equal(one.view(torch.int16), two.view(torch.int16))
+
+
 def test_zero_length_sequences_and_empty_batch():
     from triton_op_b200.inputs import DecodeConfig, make_inputs
     cfg = DecodeConfig("zeros", 5, 8, 2, 16, 1, ("fixed", 100))
@@ -237,19 +273,21 @@ def test_llama8b_shape_full_size_against_oracle_on_device():
 
 # ----------------------------------------------------------------------------- reference test matrix
 # test_pa_mtp.py:48-54 of the reference: block sizes {16, 64, 1024}, (Hq, Hkv) in {(5,1), (8,1),
-# (10,1), (16,1), (64,4)}, query length 1-4, context {512, 4096, 4097}; here at batch 3, uniform
-# data as in that harness, per-token scales (what the harness feeds the Gluon kernel), with the
-# oracle run on the GPU.
+# (10,1), (16,1), (64,4)}, query length 1-4, context {512, 4096, 4097}, batch {4, 80, 128}, and the
+# whole sweep again with the shuffled value layout (--trans_v).  Here every shape runs at batch 3
+# in both value layouts, uniform data as in that harness, per-token scales (what the harness feeds
+# the Gluon kernel), with the oracle run on the GPU; batches 80 and 128 follow below.
 _MATRIX = [(bs, hq, hkv, ql, ctx)
            for bs in (16, 64, 1024)
            for (hq, hkv) in ((5, 1), (8, 1), (10, 1), (16, 1), (64, 4))
            for ql in (1, 2, 3, 4)
-           for ctx in (512, 4097)]
+           for ctx in (512, 4096, 4097)]
 
 
 @pytest.mark.parametrize("bs,hq,hkv,ql,ctx", _MATRIX)
 def test_reference_matrix(bs, hq, hkv, ql, ctx):
-    from triton_op_b200.inputs import DecodeConfig, make_inputs
+    from triton_op_b200 import paged_attention_decode
+    from triton_op_b200.inputs import DecodeConfig, make_inputs, shuffle_value_cache_layout, unpack_mtp
     cfg = DecodeConfig(f"m{bs}_{hq}_{hkv}_{ql}_{ctx}", 3, hq, hkv, bs, ql, ("fixed", ctx), quant="per_token")
     inp = make_inputs(cfg, seed=bs + hq + ql, device=DEV, dist="uniform")
     st = _status()
@@ -258,6 +296,35 @@ def test_reference_matrix(bs, hq, hkv, ql, ctx):
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     assert_close(out, ref, what=cfg.name)
+    # the same call on the shuffled value layout [NB, Hkv, bs/16, D, 16]: same products in the same order
+    out_t = torch.full_like(inp.query, float("nan"))
+    paged_attention_decode(out_t, inp.query, inp.key_cache, shuffle_value_cache_layout(inp.value_cache), inp.context_lens,
+                           inp.block_tables, inp.softmax_scale, ql, inp.max_context, torch.bfloat16, None, inp.key_scale,
+                           inp.value_scale, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert torch.equal(unpack_mtp(out_t, 3, ql, hkv), out), f"{cfg.name}: transposed value layout differs"
+
+
+@pytest.mark.parametrize("batch,bs,hq,hkv,ql,ctx", [(80, 16, 8, 1, 2, 4097), (128, 1024, 64, 4, 1, 4096),
+                                                    (128, 64, 10, 1, 3, 512), (80, 1024, 16, 1, 4, 4097)])
+def test_reference_matrix_large_batches(batch, bs, hq, hkv, ql, ctx):
+    """Batches 80 and 128 of the reference's sweep (test_pa_mtp.py:52): the oracle checks a sample of
+    the sequences, and every sequence must equal its own result in a batch of one sample."""
+    import copy
+    from triton_op_b200.inputs import DecodeConfig, make_inputs, subset_inputs
+    cfg = DecodeConfig(f"b{batch}_{bs}_{hq}_{ql}", batch, hq, hkv, bs, ql, ("fixed", ctx), quant="per_token")
+    inp = make_inputs(cfg, seed=batch + bs, device=DEV, dist="uniform")
+    st = _status()
+    out, _ = run_operator(inp, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and bool(torch.isfinite(out.float()).all())
+    pick = sorted(torch.randperm(batch, generator=torch.Generator().manual_seed(batch))[:5].tolist())
+    sub = subset_inputs(inp, pick)
+    rows = [s * ql + t for s in pick for t in range(ql)]
+    assert_close(out[rows], oracle_output(sub), what=f"{cfg.name}: sampled sequences vs oracle")
+    out_sub, _ = run_operator(sub, status=st)
+    assert torch.equal(out_sub, out[rows])
 
 
 @pytest.mark.parametrize("name,num_seqs", [("cfg3_llama70b_mtp", 12), ("cfg4_longctx", 3), ("cfg5_serving_fp8", 48),
@@ -349,32 +416,87 @@ def test_transposed_value_layout(bs, heads, ql, quant):
     assert torch.equal(unpack_mtp(out, cfg.num_seqs, ql, hkv), normal)     # same products, same order
 
 
-@pytest.mark.parametrize("heads,ql,bs,quant", [((32, 8), 1, 16, "per_tensor"), ((8, 1), 1, 64, "per_token"),
-                                               ((16, 2), 2, 1024, "per_token"), ((16, 1), 1, 16, "per_tensor"),
-                                               ((10, 1), 4, 16, "per_tensor")])
-def test_alibi_slopes(heads, ql, bs, quant):
-    """ALiBi bias slope[head] * (key position - (context - 1)) (pa_decode_triton_gluon_fp8.py:905-908);
-    the reference never tests it, so the oracle's statement of that formula is the yardstick."""
+@pytest.mark.parametrize("heads,ql,bs,quant,kv,tune", [
+    ((32, 8), 1, 16, "per_tensor", "fp8", None), ((8, 1), 1, 64, "per_token", "fp8", None),
+    ((16, 2), 2, 1024, "per_token", "fp8", None), ((16, 1), 1, 16, "per_tensor", "fp8", None),
+    ((10, 1), 4, 16, "per_tensor", "fp8", None),
+    # the mma.sync fp8 kernel (asked for explicitly) and the bf16-KV kernel
+    ((32, 8), 1, 16, "per_tensor", "fp8", {"warps": 8}), ((16, 2), 2, 16, "per_token", "fp8", {"warps": 4}),
+    ((32, 8), 1, 16, "none", "bf16", None), ((16, 2), 2, 16, "none", "bf16", None)])
+def test_alibi_slopes(heads, ql, bs, quant, kv, tune):
+    """ALiBi bias slope[head] * (key position - (context - 1)) (pa_decode_triton_gluon_fp8.py:905-908,
+    pa_decode_triton.py:148-151) on all three partition kernels, against the oracle, whose statement of
+    the bias is pinned to a run of the reference's Triton path (tests/golden/triton_*_alibi.npz)."""
     from oracle import pa_oracle
     from triton_op_b200 import paged_attention_decode
     from triton_op_b200.inputs import DecodeConfig, make_inputs, unpack_mtp
     hq, hkv = heads
-    cfg = DecodeConfig("alibi", 3, hq, hkv, bs, ql, ("fixed", 1), quant=quant)
+    cfg = DecodeConfig("alibi", 3, hq, hkv, bs, ql, ("fixed", 1), quant=quant, kv_dtype=kv)
     inp = make_inputs(cfg, seed=29, device=DEV, context_lens=torch.tensor([900, 2050, 17]))
     slopes = (2.0 ** (-8.0 * torch.arange(1, hq + 1, dtype=torch.float32) / hq)).to(DEV)   # the usual geometric slopes
     out = torch.full_like(inp.query, float("nan"))
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     res = paged_attention_decode(out, inp.query, inp.key_cache, inp.value_cache, inp.context_lens, inp.block_tables,
                                  inp.softmax_scale, ql, inp.max_context, torch.bfloat16, None, inp.key_scale,
-                                 inp.value_scale, 0, slopes, status=status)
+                                 inp.value_scale, 0, slopes, status=status, tune=tune)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     ks, vs = inp.flat_scales()
     ref = pa_oracle.paged_attention(inp.query_tokens, inp.key_cache, inp.value_cache, inp.block_tables, inp.context_lens,
                                     inp.query_indptr(), ks, vs, alibi_slopes=slopes)
     assert_close(unpack_mtp(out, cfg.num_seqs, ql, hkv), ref, what="alibi")
-    no_bias, _ = run_operator(inp)
+    no_bias, _ = run_operator(inp, tune=tune)
     assert (unpack_mtp(out, cfg.num_seqs, ql, hkv).float() - no_bias.float()).abs().max() > 1e-2   # the bias matters
+
+
+def _triton_golden(name):
+    import importlib.util, os
+    import numpy as np
+    here = os.path.join(os.path.dirname(__file__), "golden")
+    spec = importlib.util.spec_from_file_location("make_golden_triton", os.path.join(here, "make_golden_triton.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    z = np.load(os.path.join(here, name + ".npz"))
+    inp, slopes = mod.case_inputs(name)
+    return inp, slopes, {k: torch.from_numpy(z[k].copy()) for k in ("out", "tmp_output", "exp_sums", "max_logits")}
+
+
+@pytest.mark.parametrize("name", ["triton_g4", "triton_g4_alibi", "triton_g16", "triton_g16_alibi"])
+@pytest.mark.parametrize("kv", ["bf16", "fp8"])
+def test_operator_matches_the_reference_triton_run(name, kv):
+    """Output and split-KV intermediates against fixtures the reference's own Triton decode produced
+    (pa_decode_triton.py:523-685 under the Triton interpreter, fp16 arithmetic), with and without
+    ALiBi: the bf16-KV kernel on the same values, and the fp8 kernels on the values quantised per
+    tensor (then the fixture is only as close as the quantisation allows: looser bounds, stated)."""
+    from triton_op_b200 import paged_attention_decode
+    from triton_op_b200.inputs import from_paged_key, from_paged_value, quantize_per_tensor, to_paged_key, to_paged_value
+    inp, slopes, gold = _triton_golden(name)
+    inp = inp.to(DEV)
+    c = inp.cfg
+    kc, vc, ksc, vsc = inp.key_cache, inp.value_cache, None, None
+    if kv == "fp8":
+        k8, ksc = quantize_per_tensor(from_paged_key(kc).contiguous())
+        v8, vsc = quantize_per_tensor(from_paged_value(vc).contiguous())
+        kc, vc = to_paged_key(k8), to_paged_value(v8)
+    out = torch.full_like(inp.query, float("nan"))
+    st = _status()
+    res = paged_attention_decode(out, inp.query, kc, vc, inp.context_lens, inp.block_tables, inp.softmax_scale, 1,
+                                 inp.max_context, torch.bfloat16, None, ksc, vsc, 0,
+                                 None if slopes is None else slopes.to(DEV), status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    # bf16 KV: the same values as the reference saw; tolerance = this build's bar for bf16 outputs.
+    # fp8 KV: e4m3 keeps 4 significant bits of each key / value element; the per-element noise
+    # averages out over the head dimension and the context, one e4m3 element is off by up to 6 %, and ALiBi with a steep slope makes an output row nearly one value row.
+    atol, rtol = (ATOL, RTOL) if kv == "bf16" else (6e-2, 7e-2)
+    assert_close(out, gold["out"], atol=atol, rtol=rtol, what=f"{name} {kv}: output")
+    m, l, o = res["maximum_logits"].cpu(), res["exponential_sums"].cpu(), res["temporary_output"].float().cpu()
+    if kv == "bf16":
+        for s in range(c.num_seqs):
+            np_s = (int(inp.context_lens[s]) + 255) // 256
+            assert torch.allclose(m[s, :, :np_s], gold["max_logits"][s, :, :np_s], atol=1e-2, rtol=2e-3)
+            assert torch.allclose(l[s, :, :np_s], gold["exp_sums"][s, :, :np_s], atol=1e-3, rtol=1e-2)
+            assert torch.allclose(o[s, :, :np_s], gold["tmp_output"][s, :, :np_s], atol=ATOL, rtol=RTOL)
 
 
 @pytest.mark.parametrize("heads,ql,bs,kv", [((32, 8), 1, 16, "fp8"), ((16, 2), 2, 1024, "fp8"), ((8, 2), 1, 16, "bf16")])

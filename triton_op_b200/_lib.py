@@ -10,7 +10,7 @@ import os
 
 from .build import LIB_PATH
 
-PA_ABI_VERSION = 2
+PA_ABI_VERSION = 3
 
 PA_OK = 0
 PA_DT_BF16, PA_DT_E4M3FN = 0, 1
@@ -25,7 +25,7 @@ EXPORTS = (
     "pa_decode_sm100", "pa_decode_noalloc_sm100", "pa_partition_sm100", "pa_reduce_sm100", "pa_merge_triples_sm100",
     "pa_merge_packed_triples_sm100", "pa_packed_triple_floats", "pa_exchange_alloc", "pa_exchange_open", "pa_exchange_close", "pa_exchange_free",
     "pa_exchange_bytes", "pa_reduce_push_sm100", "pa_merge_wait_sm100",
-    "pa_cache_write_sm100", "pa_query_launch_sm100", "pa_strerror", "pa_last_cuda_error", "pa_abi_version",
+    "pa_cache_write_sm100", "pa_stream_probe_sm100", "pa_query_launch_sm100", "pa_strerror", "pa_last_cuda_error", "pa_abi_version",
 )
 
 
@@ -36,7 +36,7 @@ class PaDecodeParams(C.Structure):
         + [(n, C.c_void_p) for n in (
             "out", "query", "key_cache", "value_cache", "block_tables", "context_lens",
             "query_scale", "key_scale", "value_scale", "alibi_slopes", "sink_tokens",
-            "exp_sums", "max_logits", "tmp_out", "status", "trace")]
+            "exp_sums", "max_logits", "tmp_out", "status", "trace", "merge_counters")]
         + [(n, C.c_int32) for n in (
             "num_seqs", "num_kv_heads", "query_group_size", "query_len", "head_size",
             "block_size", "num_blocks", "max_blocks_per_seq", "partition_size", "max_partitions")]
@@ -49,7 +49,7 @@ class PaDecodeParams(C.Structure):
         + [(n, C.c_int32) for n in (
             "q_dtype", "kv_dtype", "out_dtype", "q_quant_mode", "kv_quant_mode", "v_layout")]
         + [("softmax_scale", C.c_float)]
-        + [(n, C.c_int32) for n in ("tune_warps", "tune_stages", "tune_ctas", "tune_vstages")]
+        + [(n, C.c_int32) for n in ("tune_warps", "tune_stages", "tune_ctas", "tune_vstages", "tune_fuse", "reserved0")]
     )
 
 
@@ -119,6 +119,8 @@ def lib() -> C.CDLL:
         getattr(L, name).restype = C.c_int
     L.pa_cache_write_sm100.argtypes = [C.POINTER(PaCacheWriteParams), C.c_void_p]
     L.pa_cache_write_sm100.restype = C.c_int
+    L.pa_stream_probe_sm100.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
+    L.pa_stream_probe_sm100.restype = C.c_int
     for name in ("pa_decode_sm100", "pa_decode_noalloc_sm100", "pa_partition_sm100", "pa_reduce_sm100",
                  "pa_merge_triples_sm100", "pa_query_launch_sm100", "pa_last_cuda_error",
                  "pa_abi_version"):

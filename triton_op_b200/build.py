@@ -16,7 +16,7 @@ LIB_DIR = os.path.join(PKG_DIR, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libpa_decode_sm100.so")
 SOURCES = ["pa_decode_sm100.cu"]
 HEADERS = ["pa_common.cuh", "pa_params.cuh", "pa_partition_fp8.cuh", "pa_partition_bf16.cuh", "pa_partition_tc.cuh", "pa_tcgen05.cuh",
-           "pa_reduce.cuh", "pa_cache_write.cuh", "pa_exchange.cuh",
+           "pa_reduce.cuh", "pa_cache_write.cuh", "pa_exchange.cuh", "pa_stream_probe.cuh",
            os.path.join("..", "..", "include", "pa_decode_sm100.h")]
 
 NVCC_FLAGS = [

@@ -206,6 +206,14 @@ __device__ __forceinline__ void split_hi_lo(float x, float& hi, float& lo) {
   lo = (x - hi) * 16.0f;
 }
 
+// The same split with the low part unscaled (x = hi + lo) when UNSCALED: for operands whose two
+// parts are multiplied separately and added by the tensor core itself.
+template <bool UNSCALED>
+__device__ __forceinline__ void split_parts(float x, float& hi, float& lo) {
+  hi = __uint_as_float(__float_as_uint(x) & 0xfff00000u);
+  lo = UNSCALED ? x - hi : (x - hi) * 16.0f;
+}
+
 __device__ __forceinline__ float bf16_lo_to_f32(uint32_t packed) {
   return __uint_as_float(packed << 16);
 }

@@ -15,6 +15,7 @@
 #include "pa_reduce.cuh"
 #include "pa_cache_write.cuh"
 #include "pa_exchange.cuh"
+#include "pa_stream_probe.cuh"
 
 namespace {
 
@@ -102,6 +103,7 @@ struct LaunchPlan {
   int mtiles = 0;     // 8-row query tiles per warp
   bool per_token = false;
   bool tensor_path = false;  // tcgen05 kernel (else the mma.sync kernel)
+  bool fused = false;        // tcgen05 kernel in its single-launch form: it also merges the partitions
   bool bf16_kv = false;      // bf16 KV cache (mma.sync bf16 kernel)
   int rows = 0;              // query rows per work item (tcgen05 kernel)
   int grid = 0;
@@ -138,7 +140,9 @@ int validate(const PaDecodeParams* p, bool need_partition_inputs, bool need_out)
   return PA_OK;
 }
 
-int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
+// allow_fuse: the caller wants the whole decode (partitions and their merge) and would take it as
+// one launch where the kernel has that form.
+int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false) {
   int rc = validate(p, true, false);
   if (rc != PA_OK) return rc;
   DeviceInfo* dev = nullptr;
@@ -158,13 +162,12 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
   const bool v_trans = p->v_layout == PA_V_TRANSPOSED && p->block_size != 16;
   if (p->v_layout != PA_V_NORMAL && p->v_layout != PA_V_TRANSPOSED) return PA_ERR_UNSUPPORTED;
   if (p->v_layout == PA_V_TRANSPOSED && p->kv_dtype != PA_DT_E4M3FN) return PA_ERR_UNSUPPORTED;
-  // (ALiBi: tcgen05 kernel only, checked below)
   if (eqG > 64) return PA_ERR_UNSUPPORTED;
   // tcgen05 kernel: 256-token partitions.  tune_warps == 4 / 8 explicitly asks for the mma.sync
   // kernel, which also covers other partition sizes for 16-token pages and up to 16 query rows.
   const bool tensor_path = !bf16_kv && p->partition_size == pa::tc::kItemTokens && p->tune_warps == 0;
   if (!tensor_path) {
-    if (p->block_size != 16 || eqG > 16 || q_item != 2 || p->alibi_slopes) return PA_ERR_UNSUPPORTED;
+    if (p->block_size != 16 || eqG > 16 || q_item != 2) return PA_ERR_UNSUPPORTED;
     if (p->partition_size % (bf16_kv ? pa::kPageTokens : pa::kStageTokens) != 0 ||
         p->partition_size / p->block_size > 32)
       return PA_ERR_UNSUPPORTED;
@@ -256,6 +259,18 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan) {
     plan->rows = qr;
     k.num_row_blocks = nrb;
     plan->warps = pa::tc::kThreads / 32;
+    // Single launch: one row block per (partition, head), every row's partitions within one chunk
+    // of the merge (32), and a counter array to tell the last partition of a row set from the others.
+    plan->fused = allow_fuse && p->merge_counters != nullptr && p->out != nullptr && nrb == 1 && qr <= 8 &&
+                  p->max_partitions <= 32 && p->alibi_slopes == nullptr && p->trace == nullptr && p->tune_fuse > 0;
+    if (plan->fused) {
+      plan->warps = pa::tc::kThreadsFused / 32;
+      k.out = static_cast<uint8_t*>(p->out);
+      k.sink = p->sink_tokens;
+      k.merge_counters = p->merge_counters;
+      k.out_stride_seq = p->out_stride_seq;
+      k.out_stride_head = p->out_stride_head;
+    }
     int off = pa::tc::kHeadBytes;
     k.off_seq_offsets = off;
     k.off_seq_ctx = off + round_up((p->num_seqs + 1) * 4, 16);
@@ -342,9 +357,9 @@ int launch_partition_t(const LaunchPlan& plan, cudaStream_t stream) {
   return PA_OK;
 }
 
-template <int BS, int QR, bool PT, bool TRACE, bool ALIBI = false>
+template <int BS, int QR, bool PT, bool TRACE, bool ALIBI = false, bool FUSE = false>
 int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
-  auto kern = pa::tc::pa_partition_fp8_tc_kernel<BS, QR, PT, TRACE, ALIBI>;
+  auto kern = pa::tc::pa_partition_fp8_tc_kernel<BS, QR, PT, TRACE, ALIBI, FUSE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
   if (e != cudaSuccess) return cuda_fail(e);
   // Programmatic dependent launch: in a decode loop the CTAs may become resident and set up their
@@ -352,7 +367,7 @@ int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
   // reduce) drains; the kernel waits (griddepcontrol.wait) before it reads or writes global memory.
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)plan.grid);
-  cfg.blockDim = dim3(pa::tc::kThreads);
+  cfg.blockDim = dim3(FUSE ? pa::tc::kThreadsFused : pa::tc::kThreads);
   cfg.dynamicSmemBytes = (size_t)plan.smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -370,6 +385,13 @@ int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
 template <int BS, bool TRACE>
 int launch_tensor_bs(const LaunchPlan& plan, cudaStream_t stream) {
   const bool pt = plan.per_token;
+  if (!TRACE && plan.fused) {                 // the single-launch instantiations (4 or 8 rows per item)
+    if (plan.rows == 4)
+      return pt ? launch_tensor_t<BS, 4, true, false, false, true>(plan, stream) : launch_tensor_t<BS, 4, false, false, false, true>(plan, stream);
+    if (plan.rows == 8)
+      return pt ? launch_tensor_t<BS, 8, true, false, false, true>(plan, stream) : launch_tensor_t<BS, 8, false, false, false, true>(plan, stream);
+    return PA_ERR_UNSUPPORTED;
+  }
   if (!TRACE && plan.kp.alibi != nullptr) {   // the ALiBi instantiations
     switch (plan.rows) {
       case 4: return pt ? launch_tensor_t<BS, 4, true, false, true>(plan, stream) : launch_tensor_t<BS, 4, false, false, true>(plan, stream);
@@ -515,12 +537,12 @@ int pa_reduce_sm100(const PaDecodeParams* params, float* tri_m, float* tri_l, fl
 
 int pa_decode_sm100(const PaDecodeParams* params, void* stream) {
   LaunchPlan plan;
-  int rc = make_plan(params, &plan);
+  int rc = make_plan(params, &plan, true);
   if (rc != PA_OK) return rc;
   rc = validate(params, true, true);
   if (rc != PA_OK) return rc;
   rc = launch_partition(plan, static_cast<cudaStream_t>(stream));
-  if (rc != PA_OK) return rc;
+  if (rc != PA_OK || plan.fused) return rc;   // the single-launch kernel has merged the partitions itself
   return launch_reduce(params, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
 }
 
@@ -803,10 +825,26 @@ int pa_cache_write_sm100(const PaCacheWriteParams* p, void* stream) {
   return PA_OK;
 }
 
+int pa_stream_probe_sm100(const void* a, const void* b, int64_t bytes_each, int32_t* status, void* stream) {
+  if (!a || !b) return PA_ERR_NULL_POINTER;
+  if (bytes_each <= 0 || bytes_each % pa::kProbeSlotBytes != 0) return PA_ERR_BAD_SHAPE;
+  if (!aligned16(a) || !aligned16(b)) return PA_ERR_ALIGNMENT;
+  DeviceInfo* dev = nullptr;
+  int rc = device_info(&dev);
+  if (rc != PA_OK) return rc;
+  cudaError_t e = cudaFuncSetAttribute(pa::pa_stream_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       pa::kProbeSmem);
+  if (e != cudaSuccess) return cuda_fail(e);
+  pa::pa_stream_probe_kernel<<<dev->sm_count, pa::kProbeWarps * 32, pa::kProbeSmem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(a), static_cast<const uint8_t*>(b), (long long)(bytes_each / pa::kProbeSlotBytes), status);
+  e = cudaGetLastError();
+  return e != cudaSuccess ? cuda_fail(e) : PA_OK;
+}
+
 int pa_query_launch_sm100(const PaDecodeParams* params, int32_t* grid_ctas, int32_t* cta_threads,
                           int32_t* smem_bytes, int32_t* ring_stages) {
   LaunchPlan plan;
-  int rc = make_plan(params, &plan);
+  int rc = make_plan(params, &plan, true);   // what pa_decode_sm100 would launch
   if (rc != PA_OK) return rc;
   if (grid_ctas) *grid_ctas = plan.grid;
   if (cta_threads) *cta_threads = plan.warps * 32;

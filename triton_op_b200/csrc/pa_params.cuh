@@ -24,6 +24,12 @@ struct KernelParams {
   uint8_t* tmp_out;            // bf16
   int32_t* status;             // may be null
   unsigned long long* trace;   // tuning aid: per-role clock stamps of CTA 0; null in normal operation
+  // single-launch decode (the partition kernel also merges the partitions): the final output, the
+  // optional sink logits and one counter per (sequence, kv head), zero between launches
+  uint8_t* out;                // bf16 [S, Hkv*eqG, D]; null unless the launch merges
+  const float* sink;           // [Hkv*G] or null
+  int32_t* merge_counters;     // [S*Hkv]
+  int64_t out_stride_seq, out_stride_head;   // elements
 
   // sizes
   int32_t S, Hkv, G, L, eqG;

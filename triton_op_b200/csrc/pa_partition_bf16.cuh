@@ -153,6 +153,14 @@ pa_partition_bf16_p16_kernel(const __grid_constant__ KernelParams p) {
     int lim[2];  // first token the row may not see
     lim[0] = it.ctx - (p.L - 1 - (ok0 ? g / p.G : 0));
     lim[1] = it.ctx - (p.L - 1 - (ok1 ? (g + 8) / p.G : 0));
+    // ALiBi (pa_decode_triton.py:92-99, 148-151): slope[query head] * (key position - (context - 1)) on
+    // the scaled scores; here in the base-2 logit domain
+    const bool alibi = p.alibi != nullptr;
+    float slope[2] = {0.f, 0.f};
+    if (alibi) {
+      if (ok0) slope[0] = __ldg(p.alibi + it.head * p.G + g % p.G) * kLog2e;
+      if (ok1) slope[1] = __ldg(p.alibi + it.head * p.G + (g + 8) % p.G) * kLog2e;
+    }
     __syncwarp();
     fence_proxy_async();
     if (ck + wtot < n_items) issue_query(decode_item(ck + wtot, p, seq_off, seq_ctx));
@@ -190,6 +198,7 @@ pa_partition_bf16_p16_kernel(const __grid_constant__ KernelParams p) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             float v = c[tau][2 * h + e] * row_scale;
+            if (alibi) v = fmaf(slope[h], (float)(tok - (it.ctx - 1)), v);
             if (tail && tok >= lim[h]) v = -INFINITY;
             sv[h][tau * 2 + e] = v;
           }

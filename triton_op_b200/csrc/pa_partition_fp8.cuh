@@ -296,6 +296,7 @@ pa_partition_fp8_p16_kernel(const __grid_constant__ KernelParams p) {
     uint32_t qf[MT][4][4];
     float row_scale[MT];  // softmax_scale * log2e * k_scale / (query pre-scale)
     int row_lim[MT];      // first token index the row may NOT see
+    float row_slope[MT];  // ALiBi slope of the row's query head, base-2 logit domain (0 without ALiBi)
     if (!__all_sync(kFullMask, mbar_wait(qbar, qphase))) {
       dead = true;
       break;
@@ -346,7 +347,9 @@ pa_partition_fp8_p16_kernel(const __grid_constant__ KernelParams p) {
       row_scale[mt] = p.softmax_scale * kLog2e * k_scale_t * inv_pre * qs;
       const int trow = row_ok ? r / p.G : 0;
       row_lim[mt] = it.ctx - (p.L - 1 - trow);
+      row_slope[mt] = (p.alibi != nullptr && row_ok) ? __ldg(p.alibi + it.head * p.G + r % p.G) * kLog2e : 0.f;
     }
+    const bool alibi = p.alibi != nullptr;   // bias slope * (key position - (context - 1)), pa_decode_triton_gluon_fp8.py:905-908
     __syncwarp();
     fence_proxy_async();
     if (ck + wtot < n_items) issue_query(decode_item(ck + wtot, p, seq_off, seq_ctx));
@@ -419,6 +422,7 @@ pa_partition_fp8_p16_kernel(const __grid_constant__ KernelParams p) {
           for (int i = 0; i < 4; ++i) {
             float s = fmaf(lo[i], 0.0625f, hi[i]) * row_scale[mt];
             if (PER_TOKEN) s *= ks[i];
+            if (alibi) s = fmaf(row_slope[mt], (float)(stok0 + pg * kPageTokens + 4 * t + i - (it.ctx - 1)), s);
             if (TAIL) {
               const int tok = stok0 + pg * kPageTokens + 4 * t + i;
               if (tok >= row_lim[mt]) s = -INFINITY;

@@ -48,6 +48,7 @@
 #include "pa_common.cuh"
 #include "pa_params.cuh"
 #include "pa_partition_fp8.cuh"  // build_partition_index, kPageBytes
+#include "pa_reduce.cuh"         // merge_row_one_chunk
 #include "pa_tcgen05.cuh"
 
 #include <type_traits>
@@ -67,11 +68,26 @@ constexpr int kMaxSlots = 4;
 // further ahead than the 32 KB K slots allow).
 constexpr int kQSlots = 4;
 constexpr int kWarpMma = 4 * kNG, kWarpK = 4 * kNG + 1, kWarpV = 4 * kNG + 2, kWarpQ = 4 * kNG + 3;
+// The single-launch form (FUSE) has four more warps, which merge the partitions of a (sequence,
+// kv head) once all of them are stored; see the merge warps in the kernel.  (Twenty warps leave
+// the same register budget per thread as seventeen: five warps on a scheduler either way.)
+constexpr int kWarpMerge = 4 * kNG + 4;
+constexpr int kMergeWarps = 4;
+constexpr int kThreadsFused = kThreads + 32 * kMergeWarps;
+constexpr uint32_t kMergePolls = 1u << 23;   // idle polls of a merge warp (each with a 64-200 ns sleep: about a second)
 
 // ---- geometry that depends on the rows per work item (QR = 4, 8 or 16) ---------------------------
 // Row q of the item sits in tile row / TMEM column q (hi half) and QR + q (lo half).
 __host__ __device__ constexpr int mma_n(int qr) { return qr <= 8 ? 16 : 2 * qr; }
 __host__ __device__ constexpr int q_tile_bytes(int qr) { return mma_n(qr) * kD; }  // [row block][8 chunks][8 rows][16 B]
+// With 16 rows the hi and lo halves are tiles of their own (N = 16 each), and the tensor core
+// adds the two products into the same accumulator columns: lo is then stored unscaled (x = hi +
+// lo, lo down to e4m3's subnormal step, 2^-9 against a row maximum of at least 128), the
+// accumulator has half the columns, and what a softmax thread loads from it is the logit (or
+// the output) itself.  With 4 or 8 rows both halves share one N = 16 tile and are combined in
+// registers (value = hi column + lo column / 16).
+__host__ __device__ constexpr bool sums_in_tensor_core(int qr) { return qr == 16; }
+__host__ __device__ constexpr int acc_n(int qr) { return sums_in_tensor_core(qr) ? qr : mma_n(qr); }
 // Query slot.  Its first part belongs to a query TILE (the tile and 16 floats of per-row scales),
 // the rest to a work ITEM (16-byte header: which slot holds the item's tile).  Consecutive items
 // with the same query rows share a tile, so the two parts are used as two rings with their own
@@ -89,7 +105,7 @@ constexpr int kPSbo = 288;                          // between row blocks
 __host__ __device__ constexpr int p_step_bytes(int qr) { return qr <= 8 ? 560 : 1200; }
 __host__ __device__ constexpr int p_tile_bytes(int qr) { return 8 * p_step_bytes(qr) + 64; }
 // TMEM columns of group g start at 4 * N * g: S^T (tg = 0 | 1) then O^T (parity 0 | 1), N each.
-__host__ __device__ constexpr int tmem_cols(int qr) { return 4 * mma_n(qr) * kNG <= 256 ? 256 : 512; }
+__host__ __device__ constexpr int tmem_cols(int qr) { return 4 * acc_n(qr) * kNG <= 256 ? 256 : 512; }
 
 // barrier indices inside the barrier block.
 // A parity wait is only meaningful while the waiter is at most one phase ahead of the barrier,
@@ -111,8 +127,11 @@ enum : int {
 // reads is double buffered by the item's parity inside the group.
 constexpr int kOffBars = 0;
 constexpr int kOffTmemPtr = 384;
+constexpr int kOffDone = 388;                     // [3 groups] ints: warps of the group that have stored an item (4 per item)
 constexpr int kOffScan = 400;                     // 32 ints
 constexpr int kOffRowLim = 528;                   // [64] ints: L - 1 - (row / G) for every query row
+constexpr int kOffSetsReady = 784;                // int: sets of this CTA found complete by the polling merge warp
+constexpr int kOffRowsMerged = 788;               // int: merge warps that have finished a set (4 per set)
 constexpr int kOffRedMax = 1024;                  // [4 groups][16 q][4 warps] floats
 constexpr int kOffRedSum = 2048;                  // [4 groups][2 parities][16 q][4 warps] floats
 constexpr int kOffMFin = 4096;                    // [4 groups][2 parities][16] floats (max, log2 domain)
@@ -362,12 +381,17 @@ struct Geo {
 // TRACE: compile the clock stamps in (tuning builds).
 // ALIBI: add slope[head] * (key position - (context - 1)) to the logits
 // (pa_decode_triton_gluon_fp8.py:905-908).
-template <int BS, int QR, bool PER_TOKEN, bool TRACE, bool ALIBI = false>
-__global__ void __launch_bounds__(kThreads, 1)
+// FUSE: the launch also does the cross-partition reduce (paged_attention_decode_v2_reduce_kernel,
+// pa_decode_triton_gluon_fp8.py:1187-1333): four more warps count the finished items of every
+// (sequence, kv head) in p.merge_counters and merge a row set when its last partition is stored.
+template <int BS, int QR, bool PER_TOKEN, bool TRACE, bool ALIBI = false, bool FUSE = false>
+__global__ void __launch_bounds__(FUSE ? kThreadsFused : kThreads, 1)
 pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap vmap) {
   using G = Geo<BS>;
+  static_assert(!FUSE || (QR <= 8 && !ALIBI && !TRACE), "the single-launch form exists for 4- and 8-row items");
   constexpr int NG = kNG;
-  constexpr int N = mma_n(QR);                 // MMA N and TMEM columns per tile
+  constexpr bool kSum = sums_in_tensor_core(QR);   // hi and lo products summed by the tensor core
+  constexpr int N = acc_n(QR);                 // MMA N and TMEM columns per tile
   constexpr int kQSlotBytes = q_slot_bytes(QR, PER_TOKEN);
   constexpr int kQTile = q_tile_bytes(QR);
   constexpr int kPTile = p_tile_bytes(QR);
@@ -412,13 +436,19 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     }
     mbar_fence_init();
     fence_proxy_async();
+    if (FUSE) {
+      for (int g = 0; g < NG; ++g) *reinterpret_cast<volatile int*>(smem + kOffDone + 4 * g) = 0;
+      *reinterpret_cast<volatile int*>(smem + kOffSetsReady) = 0;
+      *reinterpret_cast<volatile int*>(smem + kOffRowsMerged) = 0;
+    }
   }
   // row r = t * G + g of a kv head sees token j iff j < ctx - (L - 1 - t)
   // (padding rows of the last row block see nothing)
-  for (int r = tid; r < 64; r += kThreads) row_lim[r] = r < p.eqG ? (p.L - 1 - r / p.G) : 0x7fffffff;
+  for (int r = tid; r < 64; r += (int)blockDim.x) row_lim[r] = r < p.eqG ? (p.L - 1 - r / p.G) : 0x7fffffff;
   if (warp == kWarpMma) tmem_alloc(sbase + kOffTmemPtr, tmem_cols(QR));
   // Everything above touches this CTA's shared and tensor memory only and may run while the
-  // kernel before this one in the stream drains; from here on global memory is read and written.
+  // kernel before this one in the stream drains.
+  // From here on global memory is read and written.
   grid_dependency_wait();
   const long long t_dep = TRACE ? clock64() : 0;
   const int n_sp = build_partition_index(p, seq_off, seq_ctx, reinterpret_cast<int*>(smem + kOffScan));
@@ -429,6 +459,18 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem + kOffTmemPtr);
 
   const int n_items = n_sp * p.Hkv * p.num_row_blocks;
+  if (FUSE) {
+    // a sequence without tokens has no work item, so nobody would merge it: its output rows are zeros
+    for (int s = blockIdx.x; s < p.S; s += gridDim.x) {
+      if (seq_off[s + 1] != seq_off[s]) continue;
+      const int words = p.Hkv * p.eqG * (kD / 4);      // 8-byte words of the sequence's rows
+      for (int w = tid; w < words; w += (int)blockDim.x) {
+        const int row = w / (kD / 4), c = w - row * (kD / 4);
+        *reinterpret_cast<uint2*>(p.out + 2 * ((int64_t)s * p.out_stride_seq + (int64_t)row * p.out_stride_head + 4 * c)) =
+            make_uint2(0u, 0u);
+      }
+    }
+  }
   // items of this CTA: a contiguous range for 16-row items, else every gridDim.x-th item
   constexpr bool kContiguous = QR == 16;
   using Cursor = typename std::conditional<kContiguous, RangeCursor, ItemCursor>::type;
@@ -594,11 +636,17 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     uint4 q_next[kPasses][4];
     // A tile is built when an item's query rows are not among the tiles of the current
     // (sequence, kv head): one tile per row block, remembered until the head changes.  It goes
-    // to tile slot (tile count) % kQSlots.  That slot's previous tile is four tiles old; a
-    // (sequence, kv head) uses each of its (at most four) tiles at least once, in row-block
-    // order, so that tile's last user is at least four items back, and this loop has waited
-    // for that item's release.
+    // to tile slot (tile count) % kQSlots.  That slot's previous tile is four tiles old, and
+    // usually its last user is at least four items back, whose release this loop has waited for
+    // anyway.  Not always: a CTA whose range begins in the middle of a partition meets the row
+    // blocks in rotated order, and with three or four row blocks the tile about to be replaced
+    // may belong to an item only two or three back, whose QK^T may not even have been issued.
+    // So the loop remembers the last item that uses each tile slot and, before it rebuilds a
+    // slot, waits for that very item's release.
     int tile = -1;
+    int last_user[kQSlots];
+#pragma unroll
+    for (int s = 0; s < kQSlots; ++s) last_user[s] = -1;
     int key_seq = -1, key_head = -1;
     uint32_t tile_slots = 0;     // 4 bits per row block: bit 3 = valid, bits 0-1 = slot
     auto have_tile = [&](const TcItem& it) -> bool {
@@ -629,6 +677,22 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         tile_slots = (tile_slots & ~(15u << (4 * it.rb))) | ((8u | (uint32_t)(tile % kQSlots)) << (4 * it.rb));
       }
       const int tslot = (int)((tile_slots >> (4 * it.rb)) & 3u);
+      {
+        int lu = -1;
+#pragma unroll
+        for (int s = 0; s < kQSlots; ++s) {
+          if (s == tslot) {
+            lu = last_user[s];
+            last_user[s] = i;
+          }
+        }
+        // (the release of item lu completes phase lu / kQSlots of its slot's barrier; item lu + kQSlots,
+        // whose release would complete the next phase, has not been produced yet)
+        if (fresh && lu >= 0 && lu > i - kQSlots && !wait(bar(kBarQEmpty, lu % kQSlots), (uint32_t)(lu / kQSlots) & 1)) {
+          fail();
+          break;
+        }
+      }
       if (i + 1 < n_local) {
         cur.advance(p, seq_off);
         it_next = cur.item(p, seq_off, seq_ctx);
@@ -694,7 +758,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
                                 bf16_lo_to_f32(w[2 * k + 1]), bf16_hi_to_f32(w[2 * k + 1])};
             float hi[4], lo[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) split_hi_lo(x[e] * pre, hi[e], lo[e]);
+            for (int e = 0; e < 4; ++e) split_parts<kSum>(x[e] * pre, hi[e], lo[e]);
             hi4[k] = pack_e4m3x4(hi[0], hi[1], hi[2], hi[3]);
             lo4[k] = pack_e4m3x4(lo[0], lo[1], lo[2], lo[3]);
           }
@@ -720,6 +784,115 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarQFull, slot));
       stamp(2, i, 2);
+    }
+  } else if (FUSE && warp >= kWarpMerge) {
+    // ------------------------------------------------------------------ merge warps (single-launch form)
+    // Four warps that turn the launch into the whole decode.
+    //  * Counting (warp mw = 0).  It walks the CTA's items in order; when the softmax group of an
+    //    item has stored its partition (the group's four warps have counted themselves into
+    //    done[group]) it fences once -- which makes those stores, ordered before the fence by the
+    //    counter's release / acquire, visible to the whole GPU -- and adds one to the global counter
+    //    of the item's (sequence, kv head).  Finished items are taken in batches (lane j the j-th of
+    //    them), so a fence is paid per batch, not per item.
+    //  * Merging (all four).  The (sequence, kv head) sets are dealt to the CTAs round-robin by set
+    //    index, whoever computed their partitions: a statically dealt merge cannot pile up on the
+    //    CTAs that happen to run late, which "the last partition's CTA merges" does (a late CTA is
+    //    last for every set it touches).  Warp mw = 1 polls the counter of the CTA's next set; when
+    //    it equals the set's partition count it fences and publishes the set to the other three
+    //    through shared memory, each warp merges the rows r = mw, mw + 4 (one memory round trip per
+    //    row), and the polling warp clears the counter for the next launch once all four are done.
+    // Nothing in the pipeline ever waits for these warps; every poll of theirs is bounded.
+    if constexpr (FUSE) {
+      const int mw = warp - kWarpMerge;
+      const int n_sets = p.S * p.Hkv;
+      const uint32_t sets_ready = sbase + kOffSetsReady, rows_merged = sbase + kOffRowsMerged;
+      ItemCursor cur;
+      if (mw == 0 && n_local > 0) cur.init(first, stride, p, seq_off);
+      int i = mw == 0 ? 0 : n_local;          // next own item to count (counting warp only)
+      int j = (int)blockIdx.x;                // next set this CTA merges
+      int k = 0;                              // sets of this CTA merged so far by this warp
+      uint32_t idle = 0;
+      auto skip_empty = [&]() {
+        while (j < n_sets && seq_off[j / p.Hkv + 1] == seq_off[j / p.Hkv]) j += (int)gridDim.x;
+      };
+      skip_empty();
+      while ((i < n_local || j < n_sets) && !dead) {
+        bool progress = false;
+        if (i < n_local) {
+          const int idx = i + lane;
+          bool ok = false;
+          if (idx < n_local)
+            ok = ld_acquire_cta_shared(sbase + kOffDone + 4 * (idx % NG)) >= 4u * (uint32_t)(idx / NG + 1);
+          const unsigned mask = __ballot_sync(kFullMask, ok);
+          const int ready = mask == kFullMask ? 32 : __ffs((int)~mask) - 1;    // leading run of finished items
+          if (ready > 0) {
+            int my_set = 0;
+            for (int q = 0; q < ready; ++q) {
+              if (lane == q) my_set = cur.seq * p.Hkv + cur.head;
+              cur.advance(p, seq_off);
+            }
+            __threadfence();
+            if (lane < ready) atomicAdd(p.merge_counters + my_set, 1);
+            i += ready;
+            progress = true;
+          }
+        }
+        if (j < n_sets) {
+          const int seq = j / p.Hkv, head = j - seq * p.Hkv;
+          const int np = seq_off[seq + 1] - seq_off[seq];
+          bool go;
+          if (mw == 1) {
+            go = ld_relaxed_gpu(p.merge_counters + j) == np;
+            if (go) {
+              __threadfence();   // the partitions counted into the set are visible from here on
+              __syncwarp();
+              if (lane == 0) st_release_cta_shared(sets_ready, (uint32_t)(k + 1));
+            }
+          } else {
+            go = ld_acquire_cta_shared(sets_ready) > (uint32_t)k;
+          }
+          if (go) {
+            for (int r = mw; r < p.eqG; r += 4) {
+              const int64_t ws_row = (int64_t)seq * p.ws_stride_seq + (int64_t)head * p.ws_stride_head + r;
+              const int64_t tmp_row = (int64_t)seq * p.tmp_stride_seq + (int64_t)head * p.tmp_stride_head +
+                                      (int64_t)r * p.tmp_stride_row + 4 * lane;
+              const bool has_sink = p.sink != nullptr;
+              const float sink_logit = has_sink ? __ldg(p.sink + head * p.G + r % p.G) : 0.f;
+              merge_row_one_chunk(p.max_logits, p.exp_sums, p.tmp_out, ws_row, p.ws_stride_part, tmp_row, p.tmp_stride_part,
+                                  np, sink_logit, has_sink,
+                                  p.out + 2 * ((int64_t)seq * p.out_stride_seq + ((int64_t)head * p.eqG + r) * p.out_stride_head),
+                                  lane);
+            }
+            ++k;
+            __syncwarp();
+            if (lane == 0) red_release_cta_add(rows_merged, 1u);
+            if (mw == 1) {   // all four warps have read the set: clear its counter for the next launch
+              bool all = false;
+              for (uint32_t w = 0; w < kMergePolls && !all; ++w) {
+                all = ld_acquire_cta_shared(rows_merged) >= 4u * (uint32_t)k;
+                if (!all) __nanosleep(64);
+              }
+              if (!all) {
+                fail();
+                break;
+              }
+              if (lane == 0) p.merge_counters[j] = 0;
+            }
+            j += (int)gridDim.x;
+            skip_empty();
+            progress = true;
+          }
+        }
+        if (progress) {
+          idle = 0;
+        } else {
+          if (++idle > kMergePolls) {
+            fail();
+            break;
+          }
+          __nanosleep(mw == 0 ? 64 : 200);
+        }
+      }
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issue
@@ -751,6 +924,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
             const uint64_t ad = kd + (uint64_t)((2 * j * G::kKLbo + tg * G::kKTile1) >> 4);
             const uint64_t bd = qd + (uint64_t)(((2 * j) * 128) >> 4);
             if (leader) mma_f8_ss(d0 + tg * N, ad, bd, kIdesc, j > 0);
+            if (kSum && leader) mma_f8_ss(d0 + tg * N, ad, bd + (uint64_t)((QR / 8 * 1024) >> 4), kIdesc, true);   // the lo rows' tile
           }
         }
         if (leader) mma_commit(bar(kBarSFull, g));
@@ -776,6 +950,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           const uint64_t ad = vd + (uint64_t)((v16 ? Geo<16>::v_kstep(ks) : G::v_kstep(ks)) >> 4);
           const uint64_t bd = pd + (uint64_t)((ks * kPStep) >> 4);
           if (leader) mma_f8_ss(d0, ad, bd, kIdesc, ks > 0);
+          if (kSum && leader) mma_f8_ss(d0, ad, bd + (uint64_t)((QR / 8 * kPSbo) >> 4), kIdesc, true);   // the lo rows' tile
         }
         if (leader) mma_commit(bar(kBarOFull, ob));
         __syncwarp();
@@ -807,7 +982,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
 
     // One chunk of RC rows of a transposed accumulator tile: value = hi column + lo column / 16.
     auto load_rows = [&](uint32_t tile, int ch, uint32_t (&h)[8], uint32_t (&l)[8]) {
-      if (QR == 4) {
+      if (kSum) {
+        tmem_ld8(tile + ch * 8, h);      // the finished sums
+      } else if (QR == 4) {
         tmem_ld8(tile, h);               // columns 0-3 hi, 4-7 lo
       } else {
         tmem_ld8(tile + ch * 8, h);
@@ -815,6 +992,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       }
     };
     auto row_value = [&](const uint32_t (&h)[8], const uint32_t (&l)[8], int q) -> float {
+      if (kSum) return __uint_as_float(h[q]);
       return QR == 4 ? fmaf(__uint_as_float(h[4 + q]), 0.0625f, __uint_as_float(h[q]))
                      : fmaf(__uint_as_float(l[q]), 0.0625f, __uint_as_float(h[q]));
     };
@@ -999,8 +1177,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
             p1 = ex2(fmaf(s_keep[1][q], row_scale[q], off));
           }
           psum[q] = p0 + p1;
-          split_hi_lo(PER_TOKEN ? p0 * vs_tok[0] : p0, hi[0][q], lo[0][q]);
-          split_hi_lo(PER_TOKEN ? p1 * vs_tok[1] : p1, hi[1][q], lo[1][q]);
+          split_parts<kSum>(PER_TOKEN ? p0 * vs_tok[0] : p0, hi[0][q], lo[0][q]);
+          split_parts<kSum>(PER_TOKEN ? p1 * vs_tok[1] : p1, hi[1][q], lo[1][q]);
         }
         constexpr int W = (RC + 3) / 4;
         // tile rows: hi half at row ch * RC + q, lo half at row QR + ch * RC + q
@@ -1130,6 +1308,12 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (wq == 0) stamp(7, j, 2 * ch + 1);
       }
       fence_before_sync();  // the O^T loads are ordered before this warp's next arrival on the P barrier
+      if (FUSE) {
+        // this warp's stores of the item are issued: tell the merge warp (a release at CTA scope; the
+        // merge warp's fence makes the stores visible to the GPU, off this group's path)
+        __syncwarp();
+        if (lane == 0) red_release_cta_add(sbase + kOffDone + 4 * grp, 1u);
+      }
       if (wq == 0) stamp(5, j, 2);
       return true;
     };

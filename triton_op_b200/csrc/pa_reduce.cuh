@@ -57,6 +57,62 @@ struct ReduceParams {
   int64_t tmp_stride_seq, tmp_stride_head, tmp_stride_part, tmp_stride_row;
 };
 
+// One output row whose partitions (at most 32) all lie in one chunk, merged by one warp: the
+// arithmetic of pa_reduce_kernel<1> below, operation for operation, so that a decode call gives
+// the same bits whether its partitions are merged by that kernel or, in the single-launch form,
+// by a warp of the partition kernel itself.  Loads go to L2 (ld.global.cg): the partitions were
+// written by other SMs during the same launch.  lane owns head dims 4*lane..4*lane+3.
+__device__ __noinline__ void merge_row_one_chunk(const float* __restrict__ max_logits, const float* __restrict__ exp_sums,
+                                                 const uint8_t* __restrict__ tmp_out, int64_t ws_row, int64_t ws_stride_part,
+                                                 int64_t tmp_row, int64_t tmp_stride_part, int np, float sink_logit,
+                                                 bool has_sink, uint8_t* out_row, int lane) {
+  float m = -INFINITY, l = 0.f;
+  if (lane < np) {
+    m = __ldcg(max_logits + ws_row + (int64_t)lane * ws_stride_part);
+    l = __ldcg(exp_sums + ws_row + (int64_t)lane * ws_stride_part);
+  }
+  constexpr int kFlight = 16;
+  uint2 raw[kFlight];
+#pragma unroll
+  for (int j = 0; j < kFlight; ++j)
+    raw[j] = j < np ? __ldcg(reinterpret_cast<const uint2*>(tmp_out + 2 * (tmp_row + (int64_t)j * tmp_stride_part)))
+                    : make_uint2(0u, 0u);
+  float cm = (l > 0.f) ? m : -INFINITY;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(kFullMask, cm, o));
+  const float M = cm;
+  const float w = (l > 0.f && m > -INFINITY) ? l * expf(m - M) : 0.f;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float W = 0.f;
+  for (int j0 = 0; j0 < np; j0 += kFlight) {
+    if (j0 > 0) {
+#pragma unroll
+      for (int j = 0; j < kFlight; ++j)
+        raw[j] = (j0 + j) < np
+                     ? __ldcg(reinterpret_cast<const uint2*>(tmp_out + 2 * (tmp_row + (int64_t)(j0 + j) * tmp_stride_part)))
+                     : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int j = 0; j < kFlight; ++j) {
+      const float wj = __shfl_sync(kFullMask, w, (j0 + j) & 31);
+      if ((j0 + j) < np && wj != 0.f) {
+        W += wj;
+        acc[0] = fmaf(wj, bf16_lo_to_f32(raw[j].x), acc[0]);
+        acc[1] = fmaf(wj, bf16_hi_to_f32(raw[j].x), acc[1]);
+        acc[2] = fmaf(wj, bf16_lo_to_f32(raw[j].y), acc[2]);
+        acc[3] = fmaf(wj, bf16_hi_to_f32(raw[j].y), acc[3]);
+      }
+    }
+  }
+  float Wout = W;
+  if (has_sink && W > 0.f) Wout += expf(sink_logit - M);
+  const float inv_out = Wout > 0.f ? 1.0f / Wout : 0.f;
+  uint2 o;
+  o.x = pack_bf16x2(acc[0] * inv_out, acc[1] * inv_out);
+  o.y = pack_bf16x2(acc[2] * inv_out, acc[3] * inv_out);
+  *reinterpret_cast<uint2*>(out_row + 8 * lane) = o;
+}
+
 // WPR warps per output row (sequence, kv head, row r); lane owns head dims 4*lane..4*lane+3.
 // WPR = 1: four rows per CTA, the usual case (np <= 32: one chunk).  Long contexts have few rows
 // and hundreds of partitions each, and a single warp would walk them one memory round trip

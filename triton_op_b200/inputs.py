@@ -277,3 +277,33 @@ def make_inputs(cfg: DecodeConfig, seed: int = 0, device="cpu", num_seqs: Option
                         block_tables.to(device), ctx.to(device), 1.0 / math.sqrt(d),
                         int(ctx.max().item()) if cfg.num_seqs else 0,
                         {"pool_blocks": pool, "used_blocks": used, "seed": seed, "dist": dist})
+
+
+def subset_inputs(inp: DecodeInputs, seq_ids) -> DecodeInputs:
+    """``inp`` restricted to the sequences ``seq_ids``, with only their pages kept and renumbered
+    (page ``i`` of the result is the ``i``-th page the kept sequences use).  The bytes every kept
+    sequence sees are unchanged, so a result computed on the subset equals the rows of the full
+    batch; the pool shrinks from gigabytes to what a few sequences need, which is what a parity
+    check of a sampled handful of sequences wants to move to the host."""
+    ids = [int(i) for i in seq_ids]
+    cfg = inp.cfg
+    bs, L = cfg.block_size, cfg.query_len
+    ctx = inp.context_lens[ids].cpu()
+    nblk = ((ctx.to(torch.int64) + bs - 1) // bs).tolist()
+    rows = inp.block_tables[ids].cpu()
+    pages = torch.cat([rows[i, :n] for i, n in enumerate(nblk)] + [rows.new_zeros(0)]).long()
+    if pages.numel() == 0:
+        pages = torch.zeros(1, dtype=torch.long)
+    tables = torch.zeros((len(ids), max(1, max(nblk, default=1))), dtype=torch.int32)
+    off = 0
+    for i, n in enumerate(nblk):
+        tables[i, :n] = torch.arange(off, off + n, dtype=torch.int32)
+        off += n
+    dev = inp.key_cache.device
+    pg = pages.to(dev)
+    pick = lambda t: t if (t is None or t.dim() == 0) else t[pg]
+    tok_rows = [s * L + t for s in ids for t in range(L)]
+    sub_cfg = DecodeConfig(**{**cfg.__dict__, "num_seqs": len(ids), "pool_blocks": None})
+    return DecodeInputs(sub_cfg, inp.query[ids], inp.query_tokens[tok_rows], inp.key_cache[pg], inp.value_cache[pg],
+                        pick(inp.key_scale), pick(inp.value_scale), tables.to(dev), ctx.to(dev), inp.softmax_scale,
+                        int(ctx.max().item()) if len(ids) else 0, dict(inp.meta, subset_of=ids))

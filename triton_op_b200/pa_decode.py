@@ -77,6 +77,24 @@ def get_workspaces(num_seqs: int, num_kv_heads: int, max_partitions: int, eq_gro
     return ws
 
 
+_COUNTERS: Dict[Tuple, torch.Tensor] = {}
+
+
+def get_merge_counters(tmp_output: torch.Tensor, num_seqs: int, num_kv_heads: int) -> torch.Tensor:
+    """The ``[num_seqs * num_kv_heads]`` int32 zeros that let a decode call run as one launch
+    (``PaDecodeParams.merge_counters``), one array per workspace set: calls that share workspaces
+    must not overlap anyway, and calls on different workspaces get different counters.  The kernel
+    leaves them zero, so they are cleared only here, when they are made."""
+    key = (str(tmp_output.device), tmp_output.data_ptr(), num_seqs * num_kv_heads)
+    t = _COUNTERS.get(key)
+    if t is None:
+        if len(_COUNTERS) > 64:
+            _COUNTERS.clear()       # blocks built earlier keep their own arrays alive
+        t = torch.zeros(max(1, num_seqs * num_kv_heads), dtype=torch.int32, device=tmp_output.device)
+        _COUNTERS[key] = t
+    return t
+
+
 def _scalar_on_device(value: float, device: torch.device) -> torch.Tensor:
     key = (float(value), str(device))
     t = _SCALARS.get(key)
@@ -170,7 +188,7 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
             # a private copy: callers keep and edit their block (tuning sweeps, the no-allocation
             # entry point's tests), and the cached one must stay as validated
             return PaDecodeParams.from_buffer_copy(p), (output, query, key_cache, value_cache, sequence_lengths, block_tables, query_scale,
-                       key_scale, value_scale, alibi_slopes) + ws + (status,)
+                       key_scale, value_scale, alibi_slopes) + ws[:3] + (status,) + ws[3:]
     p, keep, cacheable = _build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
                                        softmax_scale, query_sequence_length, max_sequence_length, compute_type,
                                        query_scale, key_scale, value_scale, alibi_slopes, partition_size,
@@ -178,7 +196,7 @@ def build_params(output, query, key_cache, value_cache, sequence_lengths, block_
     if key is not None and cacheable:
         if len(_PARAM_CACHE) >= 16:
             _PARAM_CACHE.clear()
-        _PARAM_CACHE[key] = (PaDecodeParams.from_buffer_copy(p), keep[10:13])    # the block and the workspaces it points into
+        _PARAM_CACHE[key] = (PaDecodeParams.from_buffer_copy(p), keep[10:13] + keep[14:])    # the block, the workspaces and counters it points into
     return p, keep
 
 
@@ -343,6 +361,10 @@ def _build_params(output, query, key_cache, value_cache, sequence_lengths, block
         p.sink_tokens = sink_tokens.data_ptr()
     p.exp_sums, p.max_logits, p.tmp_out = exp_sums.data_ptr(), max_logits.data_ptr(), tmp_output.data_ptr()
     p.status = status.data_ptr() if status is not None else None
+    counters = None
+    if tune and tune.get("fuse", 0) > 0 and num_seqs > 0:
+        counters = get_merge_counters(tmp_output, num_seqs, num_kv_heads)
+        p.merge_counters = counters.data_ptr()
     p.trace = tune["trace"].data_ptr() if tune and tune.get("trace") is not None else None
     p.num_seqs, p.num_kv_heads, p.query_group_size = num_seqs, num_kv_heads, group
     p.query_len, p.head_size, p.block_size = query_sequence_length, head_size, kv_block_size
@@ -367,8 +389,9 @@ def _build_params(output, query, key_cache, value_cache, sequence_lengths, block
         p.tune_stages = int(tune.get("stages", 0))
         p.tune_ctas = int(tune.get("ctas", 0))
         p.tune_vstages = int(tune.get("vstages", 0))
+        p.tune_fuse = int(tune.get("fuse", 0))
     keep = (output, query, key_cache, value_cache, sequence_lengths, block_tables, q_scale_t, k_scale_t,
-            v_scale_t, alibi_slopes, exp_sums, max_logits, tmp_output, status)
+            v_scale_t, alibi_slopes, exp_sums, max_logits, tmp_output, status, counters)
     # copies made above (contiguous query, device scalars for Python-float scales) belong to this call
     used = (query, sequence_lengths, block_tables, q_scale_t, k_scale_t, v_scale_t)
     cacheable = all(u is g or (isinstance(u, torch.Tensor) and isinstance(g, torch.Tensor)
@@ -426,6 +449,13 @@ def paged_attention_decode(
     ``temporary_output``, ``final_output``, ``exponential_sums``, ``maximum_logits``; plus
     ``partition_size``, the split the returned workspaces hold: a requested multiple of 256 runs
     as 256-token sub-partitions unless the caller passed workspaces of its own.
+
+    ``tune={"fuse": 1}`` runs the call as ONE launch where the shape allows it (e4m3fn KV, 256-token
+    partitions, at most 8 query rows per kv head, at most 32 partitions, no ALiBi): four extra
+    warps of the partition kernel merge the partitions of a (sequence, kv head) once the last of
+    them is stored, instead of the reference's second launch (pa_decode_triton_gluon_fp8.py:
+    1862-1887).  Bit-identical to the default two-launch form, and measured slower than it (the
+    last rows wait for two GPU-scope fences and a counter's round trip), so it is opt-in.
     """
     p, keep = build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
                            softmax_scale, query_sequence_length, max_sequence_length, compute_type,
