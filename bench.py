@@ -267,8 +267,7 @@ class Workload:
             gen = torch.Generator()
             gen.manual_seed(0)
             lens = draw_context_lens(cfg, gen)
-            policy = "balanced" if cfg.context[0] == "lognormal" else "contiguous"
-            mine = shard_sequences(lens.tolist(), world, policy)[rank]
+            mine = shard_sequences(lens.tolist(), world, "balanced")[rank]     # by token count
             self.global_ids = mine
             sub = type(cfg)(**{**cfg.__dict__, "num_seqs": len(mine), "pool_blocks": None})
             self.inp = make_inputs(sub, seed=rank, device=dev, context_lens=lens[mine])
@@ -555,7 +554,7 @@ def run_ours(args, rank: int, world: int, local: int):
     # ---- clock burst: the same call back to back for long enough that the 20 ms sampler sees load
     burst_us = None
     if rank == 0 or world > 1:
-        n_burst = int(min(20000, max(args.steps, 0.6 / max(ms_step * 1e-3, 1e-6))))
+        n_burst = int(min(20000, max(args.steps, args.burst_seconds / max(ms_step * 1e-3, 1e-6))))
         burst_us = w.timed(w.call, n_burst, flush=False) * 1e3
     clocks = sampler.stop() if rank == 0 else None
 
@@ -819,6 +818,8 @@ def main():
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
                     help="KV-partition sharding: triples exchanged by NVLink peer stores or by an NCCL all-gather")
     ap.add_argument("--no-graph", action="store_true", help="run the e2e step with eager launches instead of a CUDA graph")
+    ap.add_argument("--burst-seconds", type=float, default=0.6,
+                    help="length of the back-to-back burst the clock sampler watches (0 for profiler captures)")
     ap.add_argument("--num-seqs", type=int, default=0,
                     help="override the workload's batch size (profiler captures of the large workloads)")
     args = ap.parse_args()

@@ -86,11 +86,12 @@ def lib() -> C.CDLL:
     global _LIB
     if _LIB is not None:
         return _LIB
-    if not os.path.exists(LIB_PATH):
+    path = os.environ.get("PA_DECODE_LIB", LIB_PATH)      # a tuning build (e.g. with clock stamps) may be named here
+    if not os.path.exists(path):
         raise ImportError(
-            f"{LIB_PATH} is missing: the sm_100a CUDA library has not been built "
+            f"{path} is missing: the sm_100a CUDA library has not been built "
             "(run `python -m triton_op_b200.build`). There is no fallback path.")
-    L = C.CDLL(LIB_PATH)
+    L = C.CDLL(path)
     P = C.POINTER(PaDecodeParams)
     L.pa_decode_sm100.argtypes = [P, C.c_void_p]
     L.pa_partition_sm100.argtypes = [P, C.c_void_p]

@@ -88,7 +88,9 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity
 
 // Bounded wait; false when the limit ran out.  The polling loop is one shared out-of-line
 // function: inlined at every wait site (and unrolled) it made up almost half of the kernel's
-// code, and the kernels' hot loops should stay inside the instruction cache.
+// code, and the kernels' hot loops should stay inside the instruction cache.  (A tighter loop,
+// four instructions a poll in one asm block, measured slower: the waiting roles then poll more
+// often and take more issue slots from the warps that compute.)
 __device__ __noinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity) {
 #pragma unroll 1
   for (uint32_t it = 0; it < kWaitPollLimit; ++it) {
