@@ -140,3 +140,26 @@ def test_mtp_row_permutation_round_trip():
     s, h, t, g = 1, 1, 1, 2
     assert torch.equal(packed[s, h * 8 + t * 4 + g], x[s * 2 + t, h * 4 + g])
     assert torch.equal(unpack_mtp(packed, 3, 2, 2), x)
+
+
+def test_subset_inputs_keeps_every_kept_sequence_bit_for_bit():
+    """``subset_inputs`` (what the benchmark's parity check moves to the host) renumbers the pages of the
+    kept sequences only: the oracle on the subset equals the oracle's rows of the full batch."""
+    from oracle import pa_oracle
+    from triton_op_b200.inputs import DecodeConfig, make_inputs, subset_inputs
+    for cfg in (DecodeConfig("s1", 6, 8, 2, 16, 2, ("uniform", 2, 300), quant="per_token"),
+                DecodeConfig("s2", 5, 4, 1, 64, 1, ("uniform", 1, 500))):
+        inp = make_inputs(cfg, seed=5)
+        ks, vs = inp.flat_scales()
+        full = pa_oracle.paged_attention(inp.query_tokens, inp.key_cache, inp.value_cache, inp.block_tables,
+                                         inp.context_lens, inp.query_indptr(), ks, vs)
+        ids = [1, 4, 5] if cfg.num_seqs > 5 else [0, 3]
+        sub = subset_inputs(inp, ids)
+        assert sub.key_cache.shape[0] < inp.key_cache.shape[0]
+        ks, vs = sub.flat_scales()
+        part = pa_oracle.paged_attention(sub.query_tokens, sub.key_cache, sub.value_cache, sub.block_tables,
+                                         sub.context_lens, sub.query_indptr(), ks, vs)
+        L = cfg.query_len
+        rows = [s * L + t for s in ids for t in range(L)]
+        assert torch.equal(part, full[rows])
+        assert torch.equal(sub.query, inp.query[ids])
