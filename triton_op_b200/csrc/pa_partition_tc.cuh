@@ -1049,33 +1049,21 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       float row_scale[RC];
       float slope[RC];   // ALiBi only
       int lim[RC];  // row q sees token j iff (tokens from j to the end of the context) > lim[q]
-#ifdef PA_AB_CAP
-      // A token is seen by every row (more than L - 1 tokens from the end of the context), by none
-      // (past the end), or -- only the last L - 1 tokens of a context -- by some: the first two cases
-      // are one fminf against +-inf per logit; the third is patched up row by row, by the one warp
-      // of the batch's few items that holds such a token.
-      const int room_[2] = {it.ctx - (it.tok0 + tok[0]), it.ctx - (it.tok0 + tok[1])};
-      const float cap[2] = {room_[0] > 0 ? INFINITY : -INFINITY, room_[1] > 0 ? INFINITY : -INFINITY};
-      const bool zone_any = __any_sync(kFullMask, (room_[0] > 0 && room_[0] < p.L) || (room_[1] > 0 && room_[1] < p.L));
-#endif
-      // (A second copy of the logit code without the masking, for the items that lie wholly inside
-      // every row's view -- all but the last partition of a context -- saved a seventh of the
-      // instructions of a 16-row item and made it 7 % slower: this loop is bound by instruction
-      // fetch, and every copy of a block of it counts.)
+      // (This loop is bound by instruction fetch for 16-row items, and every block added to it
+      // counts, executed or not.  Measured against their absence on the 16-row MTP workload: a second
+      // copy of the logit code without the masking, for the items that lie wholly inside every row's
+      // view -- all but the last partition of a context; a seventh fewer instructions -- 7 % slower;
+      // one fminf against a per-token +-inf instead of the compare and select, with the row-wise
+      // limits patched up in a rarely taken block, 7 % slower; both passes through one copy of the
+      // logit code, no change.)
       auto load_row_consts = [&](int ch) {
 #pragma unroll
         for (int q4 = 0; q4 < RC; q4 += 4) {
           const uint4 a = lds128(aux + (ch * RC + q4) * 4);
           row_scale[q4] = __uint_as_float(a.x), row_scale[q4 + 1] = __uint_as_float(a.y);
           row_scale[q4 + 2] = __uint_as_float(a.z), row_scale[q4 + 3] = __uint_as_float(a.w);
-#ifdef PA_AB_CAP
-          if (zone_any) {
-#endif
           const uint4 b = lds128(smem_addr(row_lim) + (it.rb * QR + ch * RC + q4) * 4);
           lim[q4] = (int)b.x, lim[q4 + 1] = (int)b.y, lim[q4 + 2] = (int)b.z, lim[q4 + 3] = (int)b.w;
-#ifdef PA_AB_CAP
-          }
-#endif
           if (ALIBI) {
             const uint4 c = lds128(aux + kQSlope + (ch * RC + q4) * 4);
             slope[q4] = __uint_as_float(c.x), slope[q4 + 1] = __uint_as_float(c.y);
@@ -1117,29 +1105,16 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
             float v = row_value(h[tg], l[tg], q);
             if (PER_TOKEN) v *= ks_tok[tg];
             if (ALIBI) v = fmaf(v, row_scale[q], slope[q] * rel_pos[tg]);
-#ifdef PA_AB_CAP
-            s[tg][q] = fminf(v, cap[tg]);
-#else
             s[tg][q] = room[tg] > lim[q] ? v : -INFINITY;
-#endif
           }
         }
-#ifdef PA_AB_CAP
-        if (zone_any) {
-#pragma unroll
-          for (int tg = 0; tg < 2; ++tg) {
-#pragma unroll
-            for (int q = 0; q < RC; ++q) {
-              if (!(room[tg] > lim[q])) s[tg][q] = -INFINITY;
-            }
-          }
-        }
-#endif
       };
 
       // ---- pass 1: partition maximum of the raw logits per row (transposing shuffle reduction)
       float s_keep[2][RC];
-      auto max_part = [&](int ch) {
+#pragma unroll 1
+      for (int ch = 0; ch < NCH; ++ch) {
+        raw_logits(ch, s_keep);
         float mx[RC];
 #pragma unroll
         for (int q = 0; q < RC; ++q) mx[q] = fmaxf(s_keep[0][q], s_keep[1][q]);
@@ -1150,32 +1125,29 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           const float wm = warp_max4(mx, lane);
           if ((lane & 7) == 0) rm[((lane >> 3) & 3) * 4 + wq] = wm;
         }
-      };
-      // ---- between the passes: the group's maxima (and the largest value scale) meet in shared memory
-      float vnorm = 1.0f;
-      auto between_passes = [&]() -> bool {
-        if (PER_TOKEN) {
-          const int vk = __reduce_max_sync(kFullMask, float_to_ordered(fmaxf(vs_tok[0], vs_tok[1])));
-          if (lane == 0) v_max[grp * 4 + wq] = ordered_to_float(vk);
-        }
-        if (wq == 0) stamp(6, i, 1);
-        named_barrier_sync(bar_a, 128);
-        if (PER_TOKEN) {
-          const float4 vm4 = *reinterpret_cast<const float4*>(v_max + grp * 4);
-          vnorm = fmaxf(fmaxf(vm4.x, vm4.y), fmaxf(vm4.z, vm4.w));
-          const float vinv = vnorm > 0.f ? 1.0f / vnorm : 0.f;
-          vs_tok[0] *= vinv;
-          vs_tok[1] *= vinv;
-        }
-        // The group's P^T tile is still being read by P.V of the group's previous item until that
-        // product's commit has arrived (normally long ago).
-        if (gu > 0) {
-          const uint32_t pu = gu - 1;
-          if (!wait(bar(kBarOFull, 2 * grp + (int)(pu & 1)), (pu >> 1) & 1)) return false;
-        }
-        if (wq == 0) stamp(6, i, 2);
-        return true;
-      };
+      }
+      if (PER_TOKEN) {
+        const int vk = __reduce_max_sync(kFullMask, float_to_ordered(fmaxf(vs_tok[0], vs_tok[1])));
+        if (lane == 0) v_max[grp * 4 + wq] = ordered_to_float(vk);
+      }
+      if (wq == 0) stamp(6, i, 1);
+      named_barrier_sync(bar_a, 128);
+      float vinv = 1.0f, vnorm = 1.0f;
+      if (PER_TOKEN) {
+        const float4 vm4 = *reinterpret_cast<const float4*>(v_max + grp * 4);
+        vnorm = fmaxf(fmaxf(vm4.x, vm4.y), fmaxf(vm4.z, vm4.w));
+        vinv = vnorm > 0.f ? 1.0f / vnorm : 0.f;
+        vs_tok[0] *= vinv;
+        vs_tok[1] *= vinv;
+      }
+      // The group's P^T tile is still being read by P.V of the group's previous item until that
+      // product's commit has arrived (normally long ago).
+      if (gu > 0) {
+        const uint32_t pu = gu - 1;
+        if (!wait(bar(kBarOFull, 2 * grp + (int)(pu & 1)), (pu >> 1) & 1)) return false;
+      }
+
+      if (wq == 0) stamp(6, i, 2);
       // ---- pass 2: P = exp2(raw * factor - m) * 256, split into hi / lo e4m3, stored as P^T
       // row sums of one chunk: lane ends up with the sum of one row over the warp's 64 tokens
       auto row_sums = [&](int ch, const float (&psum)[RC]) {
@@ -1188,7 +1160,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         }
       };
       float psum[RC];
-      auto exp_part = [&](int ch) {
+#pragma unroll 1
+      for (int ch = 0; ch < NCH; ++ch) {
+        if (NCH > 1) raw_logits(ch, s_keep);  // recomputed rather than kept: registers
         uint32_t pbytes[2][2 * ((RC + 3) / 4)];  // [tg][hi words, lo words], row q = byte q % 4
         float hi[2][RC], lo[2][RC];
 #pragma unroll
@@ -1228,24 +1202,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           }
         }
         if (NCH > 1) row_sums(ch, psum);
-      };
-      if constexpr (NCH == 1) {
-        raw_logits(0, s_keep);
-        max_part(0);
-        if (!between_passes()) return false;
-        exp_part(0);
-      } else {
-        // Two chunks of rows: the logits are computed again for the second pass rather than kept
-        // (registers), and both passes run through ONE copy of that code -- this loop is bound by
-        // instruction fetch, and a second inlined copy costs more than the branch below.
-#pragma unroll 1
-        for (int step = 0; step < 2 * NCH; ++step) {
-          const int ch = step % NCH;
-          if (step == NCH && !between_passes()) return false;
-          raw_logits(ch, s_keep);
-          if (step < NCH) max_part(ch);
-          else exp_part(ch);
-        }
       }
       // thread `row` of the group keeps the row's maximum (base-2 logit domain) for the epilogue
       if (r < QR) {
