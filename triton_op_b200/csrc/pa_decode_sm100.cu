@@ -491,13 +491,13 @@ int launch_reduce(const PaDecodeParams* p, float* tri_m, float* tri_l, float* tr
   if (rows == 0) return PA_OK;
   // warps per row: one while a row has at most one chunk of 32 partitions, more for long contexts
   const int wpr = r.max_partitions <= 32 ? 1 : (r.max_partitions <= 128 ? 4 : 16);
-  const int64_t blocks = wpr == 1 ? (rows + 3) / 4 : rows;
+  const int64_t blocks = wpr == 16 ? rows : (rows + 3) / 4;   // four rows per CTA, or one row of sixteen warps
   if (blocks > 0x7fffffff) return PA_ERR_TOO_LARGE;
   // Programmatic dependent launch: the reduce grid may be scheduled while the partition kernel
   // drains; it waits (griddepcontrol.wait) before it reads anything that kernel wrote.
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks);
-  cfg.blockDim = dim3(wpr == 16 ? 512 : 128);
+  cfg.blockDim = dim3(wpr == 1 ? 128 : 512);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

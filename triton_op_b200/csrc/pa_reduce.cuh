@@ -116,11 +116,14 @@ __device__ __noinline__ void merge_row_one_chunk(const float* __restrict__ max_l
 // WPR warps per output row (sequence, kv head, row r); lane owns head dims 4*lane..4*lane+3.
 // WPR = 1: four rows per CTA, the usual case (np <= 32: one chunk).  Long contexts have few rows
 // and hundreds of partitions each, and a single warp would walk them one memory round trip
-// after the other; with WPR = 4 or 16 the warps of a CTA take the 32-partition chunks of ONE row
-// round-robin and combine their running (max, sum, weighted output) through shared memory.
+// after the other; with WPR = 4 or 16 the warps of a row take its 32-partition chunks round-robin
+// and combine their running (max, sum, weighted output) through shared memory.  A CTA of the
+// multi-warp forms has 16 warps: four rows of four warps, or one row of sixteen (a serving mix with
+// a few long contexts among thousands of short rows would otherwise be one small CTA per row,
+// and the launch of tens of thousands of CTAs is then what the kernel takes).
 template <int WPR>
-__global__ void __launch_bounds__(WPR == 16 ? 512 : 128) pa_reduce_kernel(const __grid_constant__ ReduceParams p) {
-  constexpr int kWarps = WPR == 16 ? 16 : 4;
+__global__ void __launch_bounds__(WPR == 1 ? 128 : 512) pa_reduce_kernel(const __grid_constant__ ReduceParams p) {
+  constexpr int kWarps = WPR == 1 ? 4 : 16;
   constexpr int kRowsPerCta = kWarps / WPR;
   // the next kernel in the stream (the next step's partition kernel) may become resident now; it
   // waits for this grid to finish before it touches global memory
@@ -128,14 +131,18 @@ __global__ void __launch_bounds__(WPR == 16 ? 512 : 128) pa_reduce_kernel(const 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int slice = warp % WPR;
-  const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + warp / WPR;
+  const int slot = warp / WPR;      // which of the CTA's rows
+  const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + slot;
   const int64_t n_rows = (int64_t)p.S * p.Hkv * p.eqG;
-  if (row >= n_rows) return;   // WPR > 1: one row per CTA, so the whole CTA leaves together
+  // Rows past the end: a one-warp row simply leaves; the warps of a multi-warp row stay for the
+  // block-wide barrier below and walk zero partitions.
+  const bool active = row < n_rows;
+  if (WPR == 1 && !active) return;
   const int r = (int)(row % p.eqG);
   const int head = (int)((row / p.eqG) % p.Hkv);
-  const int seq = (int)(row / ((int64_t)p.eqG * p.Hkv));
+  const int seq = active ? (int)(row / ((int64_t)p.eqG * p.Hkv)) : 0;
 
-  int ctx = p.context_lens[seq];
+  int ctx = active ? p.context_lens[seq] : 0;
   ctx = max(0, min(ctx, p.ctx_cap));
   int np = (ctx + p.partition_size - 1) / p.partition_size;
   np = min(np, p.max_partitions);
@@ -208,25 +215,25 @@ __global__ void __launch_bounds__(WPR == 16 ? 512 : 128) pa_reduce_kernel(const 
     __shared__ float s_m[kWarps], s_w[kWarps];
     __shared__ float4 s_acc[kWarps][32];
     if (lane == 0) {
-      s_m[slice] = M;
-      s_w[slice] = W;
+      s_m[warp] = M;
+      s_w[warp] = W;
     }
-    s_acc[slice][lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    s_acc[warp][lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     __syncthreads();
-    if (slice != 0) return;
+    if (slice != 0 || !active) return;
     float mx = -INFINITY;
 #pragma unroll
-    for (int s = 0; s < WPR; ++s) mx = fmaxf(mx, s_m[s]);
+    for (int s = 0; s < WPR; ++s) mx = fmaxf(mx, s_m[slot * WPR + s]);
     W = 0.f;
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[e] = 0.f;
 #pragma unroll
     for (int s = 0; s < WPR; ++s) {
-      const float ms = s_m[s];
+      const float ms = s_m[slot * WPR + s];
       if (!(ms > -INFINITY)) continue;    // that warp saw no partition with weight
       const float f = expf(ms - mx);
-      const float4 a = s_acc[s][lane];
-      W = fmaf(s_w[s], f, W);
+      const float4 a = s_acc[slot * WPR + s][lane];
+      W = fmaf(s_w[slot * WPR + s], f, W);
       acc[0] = fmaf(a.x, f, acc[0]);
       acc[1] = fmaf(a.y, f, acc[1]);
       acc[2] = fmaf(a.z, f, acc[2]);
