@@ -153,7 +153,9 @@ typedef struct PaDecodeParams {
   int32_t tune_warps, tune_stages, tune_ctas, tune_vstages;
   int32_t tune_fuse;           /* 1: run pa_decode_sm100 as ONE launch where merge_counters and the shape allow it;
                                 * 0 (default): partition kernel, then reduce kernel (measured faster, see the field) */
-  int32_t reserved0;
+  int32_t tune_early;          /* -1: the tcgen05 kernel reads nothing before its dependency wait; 0 (default): it builds
+                                * its partition index from the context lengths before the wait and checks it
+                                * against them after it */
 } PaDecodeParams;
 
 /* Partition kernel followed by the reduce kernel on `stream` (a cudaStream_t); one launch that

@@ -228,6 +228,48 @@ def test_single_launch_decode_on_the_benchmark_shape():
     assert torch.equal(one.view(torch.int16), two.view(torch.int16))
 
 
+def test_lengths_and_tables_written_by_the_kernel_just_before_the_call():
+    """The tcgen05 kernel builds its partition index before its dependency wait and checks it after.
+    Here the kernel right before every call in the stream rewrites the context lengths and the block
+    tables (what a serving loop's bookkeeping kernel does), alternating between two batches, with a
+    long decode call before it so that the next call's CTAs are resident early: every result must be
+    the one for the lengths and tables as written."""
+    from triton_op_b200 import paged_attention_decode
+    from triton_op_b200.inputs import DecodeConfig, make_inputs, unpack_mtp
+    cfg = DecodeConfig("early", 48, 32, 8, 16, 1, ("uniform", 1, 3000))
+    a = make_inputs(cfg, seed=51, device=DEV)
+    b = make_inputs(cfg, seed=52, device=DEV)           # other lengths, other tables, same pool size or smaller
+    nb = min(a.key_cache.shape[0], b.key_cache.shape[0])
+    width = max(a.block_tables.shape[1], b.block_tables.shape[1])
+    pad = lambda t: torch.nn.functional.pad(t, (0, width - t.shape[1]))
+    tables = [pad(a.block_tables) % nb, pad(b.block_tables) % nb]
+    lens = [a.context_lens, b.context_lens]
+    kc, vc = a.key_cache[:nb], a.value_cache[:nb]
+    cur_tables, cur_lens = tables[0].clone(), lens[0].clone()
+    max_ctx = int(max(int(lens[0].max()), int(lens[1].max())))
+    want = []
+    for v in range(2):
+        out = torch.empty_like(a.query)
+        paged_attention_decode(out, a.query, kc, vc, lens[v].clone(), tables[v].clone(), a.softmax_scale, 1, max_ctx,
+                               torch.bfloat16, None, a.key_scale, a.value_scale, tune={"early": -1})
+        want.append(out.clone())
+    torch.cuda.synchronize()
+    st = _status()
+    outs = []
+    for it in range(40):
+        v = (it * 7 + it // 3) % 2
+        out = torch.empty_like(a.query)
+        cur_lens.copy_(lens[v])            # kernels in the same stream, directly before the call
+        cur_tables.copy_(tables[v])
+        paged_attention_decode(out, a.query, kc, vc, cur_lens, cur_tables, a.softmax_scale, 1, max_ctx, torch.bfloat16, None,
+                               a.key_scale, a.value_scale, status=st)
+        outs.append((v, out))
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    for v, out in outs:
+        assert torch.equal(out.view(torch.int16), want[v].view(torch.int16))
+
+
 def test_zero_length_sequences_and_empty_batch():
     from triton_op_b200.inputs import DecodeConfig, make_inputs
     cfg = DecodeConfig("zeros", 5, 8, 2, 16, 1, ("fixed", 100))

@@ -49,7 +49,7 @@ class PaDecodeParams(C.Structure):
         + [(n, C.c_int32) for n in (
             "q_dtype", "kv_dtype", "out_dtype", "q_quant_mode", "kv_quant_mode", "v_layout")]
         + [("softmax_scale", C.c_float)]
-        + [(n, C.c_int32) for n in ("tune_warps", "tune_stages", "tune_ctas", "tune_vstages", "tune_fuse", "reserved0")]
+        + [(n, C.c_int32) for n in ("tune_warps", "tune_stages", "tune_ctas", "tune_vstages", "tune_fuse", "tune_early")]
     )
 
 

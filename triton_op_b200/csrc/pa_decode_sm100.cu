@@ -258,6 +258,7 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
     const int nrb = (eqG + qr - 1) / qr;                  // row blocks per (partition, head)
     plan->rows = qr;
     k.num_row_blocks = nrb;
+    k.early_start = p->tune_early >= 0 ? 1 : 0;
     plan->warps = pa::tc::kThreads / 32;
     // Single launch: one row block per (partition, head), every row's partitions within one chunk
     // of the merge (32), and a counter array to tell the last partition of a row set from the others.

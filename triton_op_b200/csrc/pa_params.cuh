@@ -63,6 +63,7 @@ struct KernelParams {
   int32_t off_vring;           // V ring (tcgen05 kernel)
   int32_t num_vstages;         // V ring depth (tcgen05 kernel)
   int32_t num_row_blocks;      // ceil(eqG / rows per work item) (tcgen05 kernel)
+  int32_t early_start;         // build the partition index before the dependency wait (checked after it)
 };
 
 // Fixed head of the shared-memory carve: mbarriers and the scan scratch.

@@ -97,30 +97,40 @@ __device__ __forceinline__ Item decode_item(int k, const KernelParams& p, const 
 // can address).  Returns the total number of (sequence, partition) pairs.
 // (Run once per CTA: its loops stay rolled and it is not inlined, so that a cold start fetches a
 // few hundred bytes of it instead of ten kilobytes of unrolled divisions.)
+// A context length as the kernels use it: clamped to what the block table can address and to
+// the workspaces' partition extent.  Returns the partition count through `np`.
+__device__ __forceinline__ int clamp_context(const KernelParams& p, int c, int& np, bool& too_long) {
+  if (c > p.ctx_cap) {
+    c = p.ctx_cap;
+    too_long = true;
+  }
+  if (c < 0) c = 0;
+  np = (c + p.partition_size - 1) / p.partition_size;
+  if (np > p.max_partitions) {  // workspace extent is the hard limit
+    np = p.max_partitions;
+    c = np * p.partition_size;
+    too_long = true;
+  }
+  return c;
+}
+
+// `early`: the caller has not passed its dependency wait yet, so the lengths may still be written
+// by the kernel before this one in the stream.  They are then read past the L1 (which must not
+// keep a line that may change) and nothing is reported; the caller checks the index against the
+// lengths as they are after the wait (partition_index_still_valid) before it relies on it.
 __device__ __noinline__ int build_partition_index(const KernelParams& p, int* seq_off,
-                                                  int* seq_ctx, int* scan_scratch) {
+                                                  int* seq_ctx, int* scan_scratch, bool early = false) {
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int lane = tid & 31, warp = tid >> 5;
   if (tid == 0) seq_off[0] = 0;
   bool too_long = false;
 #pragma unroll 1
   for (int i = tid; i < p.S; i += nthr) {
-    int c = p.context_lens[i];
-    if (c > p.ctx_cap) {
-      c = p.ctx_cap;
-      too_long = true;
-    }
-    if (c < 0) c = 0;
-    int np = (c + p.partition_size - 1) / p.partition_size;
-    if (np > p.max_partitions) {  // workspace extent is the hard limit
-      np = p.max_partitions;
-      c = np * p.partition_size;
-      too_long = true;
-    }
-    seq_ctx[i] = c;
+    int np;
+    seq_ctx[i] = clamp_context(p, early ? __ldcg(p.context_lens + i) : p.context_lens[i], np, too_long);
     seq_off[i + 1] = np;
   }
-  if (too_long && p.status) atomicOr(p.status, PA_DEV_CTX_TOO_LONG);
+  if (too_long && p.status && !early) atomicOr(p.status, PA_DEV_CTX_TOO_LONG);
   __syncthreads();
   const int chunk = (p.S + nthr - 1) / nthr;
   const int beg = min(tid * chunk, p.S), end = min(beg + chunk, p.S);
@@ -145,6 +155,19 @@ __device__ __noinline__ int build_partition_index(const KernelParams& p, int* se
   }
   __syncthreads();
   return seq_off[p.S];
+}
+
+// True (for the whole CTA) when the lengths, read now, are the ones an early index was built from.
+// Also does the reporting the early build left out.  Contains a block-wide barrier.
+__device__ __noinline__ bool partition_index_still_valid(const KernelParams& p, const int* seq_ctx) {
+  bool changed = false, too_long = false;
+#pragma unroll 1
+  for (int i = threadIdx.x; i < p.S; i += blockDim.x) {
+    int np;
+    if (clamp_context(p, p.context_lens[i], np, too_long) != seq_ctx[i]) changed = true;
+  }
+  if (too_long && p.status) atomicOr(p.status, PA_DEV_CTX_TOO_LONG);
+  return __syncthreads_or(changed) == 0;
 }
 
 // MT: 8-row query tiles per warp (eqG <= 8*MT).  PER_TOKEN: per-token-per-head K/V scales.

@@ -448,10 +448,26 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   if (warp == kWarpMma) tmem_alloc(sbase + kOffTmemPtr, tmem_cols(QR));
   // Everything above touches this CTA's shared and tensor memory only and may run while the
   // kernel before this one in the stream drains.
-  // From here on global memory is read and written.
+  //
+  // So may the first link of this CTA's own chain of dependent loads (lengths -> partition index
+  // -> block-table entries -> pages), as long as nothing depends on what it reads early: the
+  // index is built from lengths read past the L1; after the wait it is checked against the
+  // lengths as they are then, and rebuilt if one changed.  In a decode loop a CTA becomes
+  // resident while the call before it drains, and one of the three memory latencies before its
+  // first bytes is then behind it when the wait returns (0.5-1 us of a call).  (Going further --
+  // requesting the pages of the CTA's first items into L2 before the wait, from block-table
+  // entries read early -- was measured and is not done: two items ahead made no difference,
+  // four cost 2 us; the traffic competes with the tail of the call before.)
+  int n_sp = 0;
+  const bool early = p.early_start != 0;
+  if (early) {
+    n_sp = build_partition_index(p, seq_off, seq_ctx, reinterpret_cast<int*>(smem + kOffScan), true);
+  }
+  // From here on global memory is read for good, and written.
   grid_dependency_wait();
   const long long t_dep = TRACE ? clock64() : 0;
-  const int n_sp = build_partition_index(p, seq_off, seq_ctx, reinterpret_cast<int*>(smem + kOffScan));
+  if (!early || !partition_index_still_valid(p, seq_ctx))
+    n_sp = build_partition_index(p, seq_off, seq_ctx, reinterpret_cast<int*>(smem + kOffScan));
   fence_before_sync();
   __syncthreads();
   fence_after_sync();

@@ -390,6 +390,7 @@ def _build_params(output, query, key_cache, value_cache, sequence_lengths, block
         p.tune_ctas = int(tune.get("ctas", 0))
         p.tune_vstages = int(tune.get("vstages", 0))
         p.tune_fuse = int(tune.get("fuse", 0))
+        p.tune_early = int(tune.get("early", 0))
     keep = (output, query, key_cache, value_cache, sequence_lengths, block_tables, q_scale_t, k_scale_t,
             v_scale_t, alibi_slopes, exp_sums, max_logits, tmp_output, status, counters)
     # copies made above (contiguous query, device scalars for Python-float scales) belong to this call
