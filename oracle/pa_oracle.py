@@ -1,7 +1,9 @@
 """CPU oracle for paged-attention decode.  TEST INFRASTRUCTURE, NOT PRODUCT CODE.
 
-Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline legs of ``bench.py`` may
-import this module; the shipped operator (``triton_op_b200``) never does.
+Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py`` (its CPU-baseline legs, where this
+module is what gets timed on host cores, and its parity checks of sampled sequences, where it is
+the checker, outside every timed region) may import this module; the shipped operator
+(``triton_op_b200``) never does.
 
 It restates, in plain torch ops that run on CPU tensors (fp32 arithmetic), the pure-PyTorch
 paged-attention path of yanguahe/triton_op, which is that repository's own correctness
