@@ -398,6 +398,29 @@ def test_long_contexts_use_the_multi_warp_reduce(lens, psize, ql):
     assert_close(out, oracle_output(inp), what=f"{lens} partition {psize}")
 
 
+def test_mixed_lengths_up_to_128_partitions():
+    """A serving-mix batch: rows of one chunk of partitions next to rows of two to four (the reduce
+    kernel that deals the further chunks of a CTA's long rows over its sixteen warps).  Against the
+    oracle, and every sequence bit-equal to itself in a smaller batch with other neighbours."""
+    from triton_op_b200.inputs import DecodeConfig, make_inputs, subset_inputs
+    lens = [20000, 300, 9000, 33, 32768, 8193, 5000, 16, 8192, 24577, 1, 12000, 700, 16385, 64, 31000, 2000, 10000]
+    cfg = DecodeConfig("mix", len(lens), 32, 8, 16, 1, ("fixed", 1))
+    inp = make_inputs(cfg, seed=61, device=DEV, context_lens=torch.tensor(lens))
+    st = _status()
+    out, res = run_operator(inp, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert 32 < res["exponential_sums"].shape[2] <= 128
+    assert_close(out, oracle_output(inp), what="mixed lengths")
+    for pick in ([0, 4, 5], [1, 2, 3, 9, 15, 17], [4]):
+        sub = subset_inputs(inp, pick)
+        if sub.max_context <= 8192:
+            continue
+        out_sub, _ = run_operator(sub, status=st)
+        assert torch.equal(out_sub, out[pick]), pick
+    assert int(st.item()) == 0
+
+
 @pytest.mark.parametrize("heads,ql,bs,kvq", [((32, 8), 1, 16, "per_tensor"), ((16, 2), 1, 16, "per_token"),
                                              ((16, 2), 2, 1024, "per_token"), ((10, 1), 3, 64, "per_tensor")])
 @pytest.mark.parametrize("qmode", ["per_tensor", "per_token"])

@@ -490,15 +490,18 @@ int launch_reduce(const PaDecodeParams* p, float* tri_m, float* tri_l, float* tr
   r.tmp_stride_row = p->tmp_stride_row;
   const int64_t rows = (int64_t)r.S * r.Hkv * r.eqG;
   if (rows == 0) return PA_OK;
-  // warps per row: one while a row has at most one chunk of 32 partitions, more for long contexts
-  const int wpr = r.max_partitions <= 32 ? 1 : (r.max_partitions <= 128 ? 4 : 16);
-  const int64_t blocks = wpr == 16 ? rows : (rows + 3) / 4;   // four rows per CTA, or one row of sixteen warps
+  if (rows > 0x7fffffff) return PA_ERR_TOO_LARGE;   // the kernels index rows with 32 bits
+  // one warp per row while a row has at most one chunk of 32 partitions (four rows per CTA); up to
+  // four chunks: eight rows per CTA whose further chunks are dealt over the CTA's warps; beyond
+  // that sixteen warps per row
+  const int wpr = r.max_partitions <= 32 ? 1 : (r.max_partitions <= 32 * pa::kMidChunks ? 4 : 16);
+  const int64_t blocks = wpr == 16 ? rows : (wpr == 4 ? (rows + pa::kMidRows - 1) / pa::kMidRows : (rows + 3) / 4);
   if (blocks > 0x7fffffff) return PA_ERR_TOO_LARGE;
   // Programmatic dependent launch: the reduce grid may be scheduled while the partition kernel
   // drains; it waits (griddepcontrol.wait) before it reads anything that kernel wrote.
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks);
-  cfg.blockDim = dim3(wpr == 1 ? 128 : 512);
+  cfg.blockDim = dim3(wpr == 1 ? 128 : (wpr == 4 ? pa::kMidRows * 32 : 512));
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -507,7 +510,7 @@ int launch_reduce(const PaDecodeParams* p, float* tri_m, float* tri_l, float* tr
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e = wpr == 1   ? cudaLaunchKernelEx(&cfg, pa::pa_reduce_kernel<1>, r)
-                  : wpr == 4 ? cudaLaunchKernelEx(&cfg, pa::pa_reduce_kernel<4>, r)
+                  : wpr == 4 ? cudaLaunchKernelEx(&cfg, pa::pa_reduce_mid_kernel, r)
                              : cudaLaunchKernelEx(&cfg, pa::pa_reduce_kernel<16>, r);
   if (e != cudaSuccess) return cuda_fail(e);
   e = cudaGetLastError();

@@ -113,70 +113,65 @@ __device__ __noinline__ void merge_row_one_chunk(const float* __restrict__ max_l
   *reinterpret_cast<uint2*>(out_row + 8 * lane) = o;
 }
 
-// WPR warps per output row (sequence, kv head, row r); lane owns head dims 4*lane..4*lane+3.
-// WPR = 1: four rows per CTA, the usual case (np <= 32: one chunk).  Long contexts have few rows
-// and hundreds of partitions each, and a single warp would walk them one memory round trip
-// after the other; with WPR = 4 or 16 the warps of a row take its 32-partition chunks round-robin
-// and combine their running (max, sum, weighted output) through shared memory.  A CTA of the
-// multi-warp forms has 16 warps: four rows of four warps, or one row of sixteen (a serving mix with
-// a few long contexts among thousands of short rows would otherwise be one small CTA per row,
-// and the launch of tens of thousands of CTAs is then what the kernel takes).
-template <int WPR>
-__global__ void __launch_bounds__(WPR == 1 ? 128 : 512) pa_reduce_kernel(const __grid_constant__ ReduceParams p) {
-  constexpr int kWarps = WPR == 1 ? 4 : 16;
-  constexpr int kRowsPerCta = kWarps / WPR;
-  // the next kernel in the stream (the next step's partition kernel) may become resident now; it
-  // waits for this grid to finish before it touches global memory
-  grid_launch_dependents();
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-  const int slice = warp % WPR;
-  const int slot = warp / WPR;      // which of the CTA's rows
-  const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + slot;
-  const int64_t n_rows = (int64_t)p.S * p.Hkv * p.eqG;
-  // Rows past the end: a one-warp row simply leaves; the warps of a multi-warp row stay for the
-  // block-wide barrier below and walk zero partitions.
-  const bool active = row < n_rows;
-  if (WPR == 1 && !active) return;
-  const int r = (int)(row % p.eqG);
-  const int head = (int)((row / p.eqG) % p.Hkv);
-  const int seq = active ? (int)(row / ((int64_t)p.eqG * p.Hkv)) : 0;
+// ---- pieces shared by the reduce kernels --------------------------------------------------------
+// Where one output row (sequence, kv head, row r) finds its partitions.
+struct RowRef {
+  int seq, head, r, np;
+  int64_t ws_base, tmp_base;   // element offsets of partition 0 (tmp_base includes this lane's 4 head dims)
+};
 
-  int ctx = active ? p.context_lens[seq] : 0;
+__device__ __forceinline__ RowRef row_ref(const ReduceParams& p, int64_t row, bool active, int lane) {
+  RowRef a;
+  // (32-bit divisions: the host refuses more than 2^31 - 1 rows, and a 64-bit division is a few
+  // hundred instructions of a kernel that is a few hundred instructions per row otherwise)
+  const unsigned row32 = (unsigned)row, per_head = (unsigned)p.eqG, per_seq = per_head * (unsigned)p.Hkv;
+  const unsigned seq_u = row32 / per_seq, in_seq = row32 - seq_u * per_seq;
+  a.head = (int)(in_seq / per_head);
+  a.r = (int)(in_seq - (unsigned)a.head * per_head);
+  a.seq = active ? (int)seq_u : 0;
+  int ctx = active ? p.context_lens[a.seq] : 0;
   ctx = max(0, min(ctx, p.ctx_cap));
-  int np = (ctx + p.partition_size - 1) / p.partition_size;
-  np = min(np, p.max_partitions);
+  a.np = min((ctx + p.partition_size - 1) / p.partition_size, p.max_partitions);
+  a.ws_base = (int64_t)a.seq * p.ws_stride_seq + (int64_t)a.head * p.ws_stride_head + a.r;
+  a.tmp_base = (int64_t)a.seq * p.tmp_stride_seq + (int64_t)a.head * p.tmp_stride_head +
+               (int64_t)a.r * p.tmp_stride_row + 4 * lane;
+  return a;
+}
 
-  const int64_t ws_base = (int64_t)seq * p.ws_stride_seq + (int64_t)head * p.ws_stride_head + r;
-  const int64_t tmp_base = (int64_t)seq * p.tmp_stride_seq + (int64_t)head * p.tmp_stride_head +
-                           (int64_t)r * p.tmp_stride_row + 4 * lane;
+// Loads from the workspaces, stated as global loads (the compiler cannot tell from a pointer inside
+// the parameter block, and generic loads cost it a handful of extra instructions each).
+__device__ __forceinline__ uint2 ld_global_u2(const void* ptr) {
+  uint2 v;
+  asm volatile("ld.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_global_f32(const void* ptr) {
+  float v;
+  asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(ptr) : "memory");
+  return v;
+}
 
-  // The launch may overlap the tail of the partition kernel (programmatic dependent launch):
-  // nothing that kernel wrote is read before this point.
-  grid_dependency_wait();
-
-  // Partitions are taken 32 at a time (lane = partition for the max / weight, then sixteen
-  // partial-output rows in flight per step) with a running maximum.  The first sixteen rows
-  // of a chunk are requested together with the maxima and sums, so the usual row (at most 16
-  // partitions) costs one memory round trip.
-  float M = -INFINITY;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  float W = 0.f;
-  for (int p0 = slice * 32; p0 < np; p0 += 32 * WPR) {
+// One warp's share of a row: the 32-partition chunks `first`, `first + step`, ... folded into a
+// running (maximum M, weight sum W, weighted output acc).  Partitions are taken 32 at a time
+// (lane = partition for the max / weight, then FLIGHT partial-output rows in flight per step).
+// The first FLIGHT rows of a chunk are requested together with the maxima and sums, so the usual
+// row (at most 16 partitions) costs one memory round trip.
+template <int FLIGHT>
+__device__ __forceinline__ void reduce_chunks(const ReduceParams& p, const RowRef& a, int first, int step, int lane,
+                                              float& M, float& W, float (&acc)[4]) {
+  for (int p0 = first * 32; p0 < a.np; p0 += 32 * step) {
     const int pi = p0 + lane;
-    const int cnt = min(32, np - p0);
+    const int cnt = min(32, a.np - p0);
     float m = -INFINITY, l = 0.f;
-    if (pi < np) {
-      m = p.max_logits[ws_base + (int64_t)pi * p.ws_stride_part];
-      l = p.exp_sums[ws_base + (int64_t)pi * p.ws_stride_part];
+    if (pi < a.np) {
+      m = ld_global_f32(p.max_logits + a.ws_base + (int64_t)pi * p.ws_stride_part);
+      l = ld_global_f32(p.exp_sums + a.ws_base + (int64_t)pi * p.ws_stride_part);
     }
-    // rows in flight: a 16-warp row has one 32-partition chunk per warp, taken in one round trip
-    constexpr int kFlight = WPR == 16 ? 32 : 16;
-    uint2 raw[kFlight];  // requested before the maximum is known
+    const uint8_t* part0 = p.tmp_out + 2 * (a.tmp_base + (int64_t)p0 * p.tmp_stride_part);   // this lane's bytes of partition p0
+    const int64_t part_bytes = 2 * p.tmp_stride_part;
+    uint2 raw[FLIGHT];  // requested before the maximum is known
 #pragma unroll
-    for (int j = 0; j < kFlight; ++j)
-      raw[j] = j < cnt ? *reinterpret_cast<const uint2*>(p.tmp_out + 2 * (tmp_base + (int64_t)(p0 + j) * p.tmp_stride_part))
-                       : make_uint2(0u, 0u);
+    for (int j = 0; j < FLIGHT; ++j) raw[j] = j < cnt ? ld_global_u2(part0 + j * part_bytes) : make_uint2(0u, 0u);
     float cm = (l > 0.f) ? m : -INFINITY;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) cm = fmaxf(cm, __shfl_xor_sync(kFullMask, cm, o));
@@ -189,16 +184,14 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 512) pa_reduce_kernel(const _
       M = newM;
     }
     const float w = (l > 0.f && m > -INFINITY) ? l * expf(m - M) : 0.f;
-    for (int j0 = 0; j0 < cnt; j0 += kFlight) {
+    for (int j0 = 0; j0 < cnt; j0 += FLIGHT) {
       if (j0 > 0) {
 #pragma unroll
-        for (int j = 0; j < kFlight; ++j)
-          raw[j] = (j0 + j) < cnt
-                       ? *reinterpret_cast<const uint2*>(p.tmp_out + 2 * (tmp_base + (int64_t)(p0 + j0 + j) * p.tmp_stride_part))
-                       : make_uint2(0u, 0u);
+        for (int j = 0; j < FLIGHT; ++j)
+          raw[j] = (j0 + j) < cnt ? ld_global_u2(part0 + (j0 + j) * part_bytes) : make_uint2(0u, 0u);
       }
 #pragma unroll
-      for (int j = 0; j < kFlight; ++j) {
+      for (int j = 0; j < FLIGHT; ++j) {
         const float wj = __shfl_sync(kFullMask, w, (j0 + j) & 31);
         if ((j0 + j) < cnt && wj != 0.f) {  // a zero-weight partition may hold anything
           W += wj;
@@ -210,40 +203,26 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 512) pa_reduce_kernel(const _
       }
     }
   }
-  if (WPR > 1) {
-    // combine the warps' partial results: warp `slice` holds (M, W, acc) of its chunks
-    __shared__ float s_m[kWarps], s_w[kWarps];
-    __shared__ float4 s_acc[kWarps][32];
-    if (lane == 0) {
-      s_m[warp] = M;
-      s_w[warp] = W;
-    }
-    s_acc[warp][lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    __syncthreads();
-    if (slice != 0 || !active) return;
-    float mx = -INFINITY;
-#pragma unroll
-    for (int s = 0; s < WPR; ++s) mx = fmaxf(mx, s_m[slot * WPR + s]);
-    W = 0.f;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) acc[e] = 0.f;
-#pragma unroll
-    for (int s = 0; s < WPR; ++s) {
-      const float ms = s_m[slot * WPR + s];
-      if (!(ms > -INFINITY)) continue;    // that warp saw no partition with weight
-      const float f = expf(ms - mx);
-      const float4 a = s_acc[slot * WPR + s][lane];
-      W = fmaf(s_w[slot * WPR + s], f, W);
-      acc[0] = fmaf(a.x, f, acc[0]);
-      acc[1] = fmaf(a.y, f, acc[1]);
-      acc[2] = fmaf(a.z, f, acc[2]);
-      acc[3] = fmaf(a.w, f, acc[3]);
-    }
-    M = mx;
-  }
+}
+
+// Folds one more warp's (maximum, weight sum, weighted output) into a combination relative to the
+// common maximum mx (the order of these calls is the order of the additions).
+__device__ __forceinline__ void fold_partial(float ms, float ws, const float4& a, float mx, float& W, float (&acc)[4]) {
+  if (!(ms > -INFINITY)) return;    // that warp saw no partition with weight
+  const float f = expf(ms - mx);
+  W = fmaf(ws, f, W);
+  acc[0] = fmaf(a.x, f, acc[0]);
+  acc[1] = fmaf(a.y, f, acc[1]);
+  acc[2] = fmaf(a.z, f, acc[2]);
+  acc[3] = fmaf(a.w, f, acc[3]);
+}
+
+// A finished row: sink weight, normalisation, and the stores (bf16 output, fp32 triple, peer lines).
+__device__ __forceinline__ void finish_row(const ReduceParams& p, const RowRef& a, int64_t row, int64_t n_rows, int lane,
+                                           float M, float W, float (&acc)[4]) {
   // sink token: a weight without a value, relative to the same maximum (triples stay without it)
   float Wout = W;
-  if (p.sink != nullptr && W > 0.f) Wout += expf(p.sink[head * p.G + r % p.G] - M);
+  if (p.sink != nullptr && W > 0.f) Wout += expf(p.sink[a.head * p.G + a.r % p.G] - M);
   const float inv = W > 0.f ? 1.0f / W : 0.f;
   const float inv_out = Wout > 0.f ? 1.0f / Wout : 0.f;
   float res[4];
@@ -252,13 +231,12 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 512) pa_reduce_kernel(const _
     res[e] = acc[e] * inv_out;
     acc[e] *= inv;
   }
-
   if (p.out) {
     uint2 o;
     o.x = pack_bf16x2(res[0], res[1]);
     o.y = pack_bf16x2(res[2], res[3]);
-    *reinterpret_cast<uint2*>(p.out + 2 * ((int64_t)seq * p.out_stride_seq +
-                                           ((int64_t)head * p.eqG + r) * p.out_stride_head + 4 * lane)) = o;
+    *reinterpret_cast<uint2*>(p.out + 2 * ((int64_t)a.seq * p.out_stride_seq +
+                                           ((int64_t)a.head * p.eqG + a.r) * p.out_stride_head + 4 * lane)) = o;
   }
   if (p.tri_o) {
     if (lane == 0) {
@@ -278,6 +256,144 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 512) pa_reduce_kernel(const _
       st_line(dst + 2 + 2 * lane, acc[2], acc[3], step);
     }
   }
+}
+
+// WPR warps per output row (sequence, kv head, row r); lane owns head dims 4*lane..4*lane+3.
+// WPR = 1: four rows per CTA, the usual case (np <= 32: one chunk).  Long contexts have few rows
+// and hundreds of partitions each, and a single warp would walk them one memory round trip
+// after the other; with WPR = 16 the warps of a CTA take the 32-partition chunks of ONE row
+// round-robin and combine their running (max, sum, weighted output) through shared memory.
+// (Rows of up to 128 partitions have a kernel of their own below.)
+template <int WPR>
+__global__ void __launch_bounds__(WPR == 1 ? 128 : 512) pa_reduce_kernel(const __grid_constant__ ReduceParams p) {
+  static_assert(WPR == 1 || WPR == 16, "one warp per row (four rows per CTA) or sixteen");
+  constexpr int kWarps = WPR == 1 ? 4 : 16;
+  constexpr int kRowsPerCta = kWarps / WPR;
+  // the next kernel in the stream (the next step's partition kernel) may become resident now; it
+  // waits for this grid to finish before it touches global memory
+  grid_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int slice = warp % WPR;
+  const int64_t row = (int64_t)blockIdx.x * kRowsPerCta + warp / WPR;
+  const int64_t n_rows = (int64_t)p.S * p.Hkv * p.eqG;
+  if (row >= n_rows) return;   // WPR = 16: one row per CTA, so the whole CTA leaves together
+  const RowRef a = row_ref(p, row, true, lane);
+
+  // The launch may overlap the tail of the partition kernel (programmatic dependent launch):
+  // nothing that kernel wrote is read before this point.
+  grid_dependency_wait();
+
+  float M = -INFINITY;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float W = 0.f;
+  // rows in flight: a 16-warp row has one 32-partition chunk per warp, taken in one round trip
+  reduce_chunks<WPR == 16 ? 32 : 16>(p, a, slice, WPR, lane, M, W, acc);
+  if (WPR > 1) {
+    // combine the warps' partial results: warp `slice` holds (M, W, acc) of its chunks
+    __shared__ float s_m[kWarps], s_w[kWarps];
+    __shared__ float4 s_acc[kWarps][32];
+    if (lane == 0) {
+      s_m[slice] = M;
+      s_w[slice] = W;
+    }
+    s_acc[slice][lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncthreads();
+    if (slice != 0) return;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < WPR; ++s) mx = fmaxf(mx, s_m[s]);
+    W = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int s = 0; s < WPR; ++s) fold_partial(s_m[s], s_w[s], s_acc[s][lane], mx, W, acc);
+    M = mx;
+  }
+  finish_row(p, a, row, n_rows, lane, M, W, acc);
+}
+
+// Rows of 33 to 128 partitions (two to four chunks) among, typically, thousands of rows of one
+// chunk: a serving mix with a few long contexts.  Eight rows per CTA, one warp each: the warp
+// reduces its row's first chunk; the further chunks of the CTA's long rows are then dealt over
+// all eight warps, and each long row's warp folds its chunks' results in chunk order.  (Four
+// warps per row, one chunk each, gives the same numbers with three of four warps idle on every
+// short row.)
+constexpr int kMidRows = 8;           // rows (= warps) per CTA
+constexpr int kMidChunks = 4;         // chunks per row at most (128 partitions)
+// one chunk of one row
+__device__ __forceinline__ void reduce_one_chunk(const ReduceParams& p, const RowRef& a, int chunk, int lane,
+                                                 float* M, float* W, float* acc) {
+  float m = -INFINITY, w = 0.f;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  reduce_chunks<16>(p, a, chunk, kMidChunks, lane, m, w, v);
+  *M = m;
+  *W = w;
+  acc[0] = v[0], acc[1] = v[1], acc[2] = v[2], acc[3] = v[3];
+}
+__global__ void __launch_bounds__(kMidRows * 32, 3) pa_reduce_mid_kernel(const __grid_constant__ ReduceParams p) {
+  __shared__ int s_extra[kMidRows];                                   // further chunks of each row
+  __shared__ float s_m[kMidRows * (kMidChunks - 1)], s_w[kMidRows * (kMidChunks - 1)];
+  __shared__ float4 s_acc[kMidRows * (kMidChunks - 1)][32];
+  grid_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int64_t row0 = (int64_t)blockIdx.x * kMidRows;
+  const int64_t row = row0 + warp;
+  const int64_t n_rows = (int64_t)p.S * p.Hkv * p.eqG;
+  const bool active = row < n_rows;
+  const RowRef a = row_ref(p, row, active, lane);
+  const int extra = active ? max(0, min((a.np + 31) / 32, kMidChunks) - 1) : 0;
+  if (lane == 0) s_extra[warp] = extra;
+  grid_dependency_wait();
+
+  // the row's first chunk
+  float M, W, acc[4];
+  reduce_one_chunk(p, a, 0, lane, &M, &W, acc);
+  __syncthreads();
+  // further chunks of the CTA's rows, numbered row by row: task t = chunk 1 + (t - first task of its row)
+  int first_task = 0, total = 0;
+#pragma unroll
+  for (int w = 0; w < kMidRows; ++w) {
+    const int e = s_extra[w];
+    if (w < warp) first_task += e;
+    total += e;
+  }
+  for (int t = warp; t < total; t += kMidRows) {
+    int owner = -1, before = 0, pre = 0;    // the row whose tasks [pre, pre + extra) hold t
+#pragma unroll
+    for (int w = 0; w < kMidRows; ++w) {
+      const int e = s_extra[w];
+      if (owner < 0 && t < pre + e) {
+        owner = w;
+        before = pre;
+      }
+      pre += e;
+    }
+    const RowRef b = row_ref(p, row0 + owner, true, lane);
+    float m2, w2, a2[4];
+    reduce_one_chunk(p, b, 1 + (t - before), lane, &m2, &w2, a2);
+    if (lane == 0) {
+      s_m[t] = m2;
+      s_w[t] = w2;
+    }
+    s_acc[t][lane] = make_float4(a2[0], a2[1], a2[2], a2[3]);
+  }
+  __syncthreads();
+  if (!active) return;
+  if (extra > 0) {   // chunk 0 from this warp's registers, then the row's further chunks in order
+    float mx = M;
+    for (int c = 0; c < extra; ++c) mx = fmaxf(mx, s_m[first_task + c]);
+    const float m0 = M, w0 = W;
+    const float4 a0 = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    W = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] = 0.f;
+    fold_partial(m0, w0, a0, mx, W, acc);
+    for (int c = 0; c < extra; ++c) fold_partial(s_m[first_task + c], s_w[first_task + c], s_acc[first_task + c][lane], mx, W, acc);
+    M = mx;
+  }
+  finish_row(p, a, row, n_rows, lane, M, W, acc);
 }
 
 // One warp per row; merges `num_shards` (m, l, o) triples.  Shard s keeps its m and l rows
