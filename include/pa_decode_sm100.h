@@ -106,13 +106,15 @@ typedef struct PaDecodeParams {
   int32_t* merge_counters;     /* optional [S*Hkv] device int32, ZERO before the first call and left zero by
                                 * every call that completes.  With it and tune_fuse = 1, pa_decode_sm100 runs as
                                 * ONE launch where it can (e4m3fn KV, partition 256, L*G <= 8, P <= 32, no
-                                * ALiBi): four extra warps of the partition kernel count the stored partitions
-                                * of every (sequence, kv head) here and merge a row set once its last
-                                * partition is in, instead of a second launch (the reference always pays that
-                                * launch, pa_decode_triton_gluon_fp8.py:1862-1887).  Same bits as the two-launch
-                                * form.  It is not the default: the end of the single launch (a GPU-scope
-                                * fence on each side of the counter before the last rows can be merged) takes
-                                * longer than the separate reduce kernel does.  One array serves one call at a
+                                * ALiBi): work items are numbered so that a CTA computes all partitions of
+                                * most (sequence, kv head) row sets and merges them itself when the last one is
+                                * stored; a set whose partitions are spread over several CTAs is merged by the
+                                * CTA that holds its first partition, and the others add their partition counts
+                                * here.  No second launch (the reference always pays that launch,
+                                * pa_decode_triton_gluon_fp8.py:1862-1887).  Same bits as the two-launch form.
+                                * It is not the default: the numbering that keeps a set inside one CTA reads
+                                * the cache measurably slower than the round-robin numbering of the two-launch
+                                * form, by more than the second launch costs.  One array serves one call at a
                                 * time; after a call that reported PA_DEV_WAIT_TIMEOUT clear it again. */
 
   /* sizes */
@@ -152,6 +154,8 @@ typedef struct PaDecodeParams {
    * tune_ctas: grid size.  For benchmarking sweeps; results do not depend on them. */
   int32_t tune_warps, tune_stages, tune_ctas, tune_vstages;
   int32_t tune_fuse;           /* 1: run pa_decode_sm100 as ONE launch where merge_counters and the shape allow it;
+                                * 1 + T: the same with teams of T CTAs sharing the kv heads of a (sequence, partition)
+                                * row (T divides num_kv_heads; default: the largest T that also divides the grid);
                                 * 0 (default): partition kernel, then reduce kernel (measured faster, see the field) */
   int32_t tune_early;          /* -1: the tcgen05 kernel reads nothing before its dependency wait; 0 (default): it builds
                                 * its partition index from the context lengths before the wait and checks it

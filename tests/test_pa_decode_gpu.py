@@ -194,9 +194,10 @@ def test_ring_depths_never_drop_below_the_issue_lag():
 
 @pytest.mark.parametrize("name", ["cfg1_small", "gqa4_ragged", "mtp2_g8", "mtp4_g2_pertoken", "pertoken_g8", "bs64_g5"])
 def test_single_launch_decode_matches_the_two_launch_form(name):
-    """tune fuse = 1: the decode call is one launch (four extra warps of the partition kernel merge a
-    row set when its last partition is stored).  Same arithmetic in the same order as the reduce
-    kernel: bit-identical outputs, counters back at zero, twice in a row."""
+    """tune fuse = 1: the decode call is one launch (the softmax group that stores the last partition
+    of a (sequence, kv head) in its CTA merges the set; sets cut by the end of a team's range are
+    handed over through the counters).  Same arithmetic in the same order as the reduce kernel:
+    bit-identical outputs, counters back at zero, twice in a row."""
     from triton_op_b200.pa_decode import get_merge_counters, query_launch
     inp = golden_inputs(name).to(DEV)
     c = inp.cfg
@@ -204,7 +205,7 @@ def test_single_launch_decode_matches_the_two_launch_form(name):
     launch = query_launch(torch.empty_like(inp.query), inp.query, inp.key_cache, inp.value_cache, inp.context_lens,
                           inp.block_tables, inp.softmax_scale, c.query_len, inp.max_context, torch.bfloat16, None,
                           inp.key_scale, inp.value_scale, tune={"fuse": 1})
-    assert launch["cta_threads"] == (20 if c.q_heads // c.kv_heads * c.query_len <= 8 else 16) * 32   # the single-launch kernel has four merge warps
+    assert launch["cta_threads"] == 16 * 32
     for _ in range(2):
         st = _status()
         one, res1 = run_operator(inp, status=st, tune={"fuse": 1})
@@ -216,16 +217,43 @@ def test_single_launch_decode_matches_the_two_launch_form(name):
     assert_close(one, load_golden(name)["out"], what=f"{name}: single launch")
 
 
-def test_single_launch_decode_on_the_benchmark_shape():
+@pytest.mark.parametrize("team", [0, 1, 2, 4])
+def test_single_launch_decode_on_the_benchmark_shape(team):
+    """Teams of 1, 2 or 4 CTAs per (sequence, partition) row (0: the library's choice): a set is
+    merged inside one CTA or handed over once, whichever way the rows are cut."""
     from triton_op_b200.inputs import CONFIGS, make_inputs
     inp = make_inputs(CONFIGS["cfg2_llama8b"], seed=3, device=DEV, num_seqs=24)
     two, _ = run_operator(inp)
     st = _status()
     for _ in range(3):
-        one, _ = run_operator(inp, status=st, tune={"fuse": 1})
+        one, _ = run_operator(inp, status=st, tune={"fuse": 1 + team})
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     assert torch.equal(one.view(torch.int16), two.view(torch.int16))
+
+
+@pytest.mark.parametrize("shape", [(2, 8000, 8, 4), (3, 8192, 2, 8), (40, 700, 8, 4), (7, 5000, 1, 8), (300, 3000, 4, 4)])
+def test_single_launch_decode_with_sets_cut_in_many_places(shape):
+    """Few long sequences: a (sequence, kv head) set of up to 32 partitions is spread over many
+    teams (a team may hold one or two rows), so most sets are merged by an owner that waits for
+    the counts of several other CTAs; many short ones: most sets lie inside one CTA; empty
+    sequences in between.  Bit-identical to the two-launch form either way."""
+    from triton_op_b200.inputs import DecodeConfig, make_inputs
+    from triton_op_b200.pa_decode import get_merge_counters
+    S, ctx, hkv, g = shape
+    cfg = DecodeConfig("cut", S, hkv * g, hkv, 16, 1, ("uniform", ctx // 3, ctx))
+    inp = make_inputs(cfg, seed=S + ctx, device=DEV)
+    if S >= 7:
+        inp.context_lens[S // 2] = 0
+        inp.context_lens[S - 1] = 0
+    two, _ = run_operator(inp)
+    st = _status()
+    for _ in range(3):
+        one, res = run_operator(inp, status=st, tune={"fuse": 1})
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert torch.equal(one.view(torch.int16), two.view(torch.int16))
+    assert int(get_merge_counters(res["temporary_output"], S, hkv).abs().sum().item()) == 0
 
 
 def test_lengths_and_tables_written_by_the_kernel_just_before_the_call():

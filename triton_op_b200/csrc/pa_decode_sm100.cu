@@ -261,11 +261,10 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
     k.early_start = p->tune_early >= 0 ? 1 : 0;
     plan->warps = pa::tc::kThreads / 32;
     // Single launch: one row block per (partition, head), every row's partitions within one chunk
-    // of the merge (32), and a counter array to tell the last partition of a row set from the others.
+    // of the merge (32), and a counter array for the row sets that are cut by the end of a team's range.
     plan->fused = allow_fuse && p->merge_counters != nullptr && p->out != nullptr && nrb == 1 && qr <= 8 &&
                   p->max_partitions <= 32 && p->alibi_slopes == nullptr && p->trace == nullptr && p->tune_fuse > 0;
     if (plan->fused) {
-      plan->warps = pa::tc::kThreadsFused / 32;
       k.out = static_cast<uint8_t*>(p->out);
       k.sink = p->sink_tokens;
       k.merge_counters = p->merge_counters;
@@ -307,7 +306,26 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
     int64_t items = items_cap * nrb;
     int64_t grid = items < dev->sm_count ? items : dev->sm_count;
     if (p->tune_ctas > 0 && p->tune_ctas < grid) grid = p->tune_ctas;
-    plan->grid = grid < 1 ? 1 : (int)grid;
+    if (grid < 1) grid = 1;
+    k.team_size = 1;
+    if (plan->fused) {
+      // teams of CTAs that share the kv heads of a (sequence, partition) row: the largest size
+      // that divides both the head count and the grid, or what the caller asks for
+      int team = p->tune_fuse > 1 ? p->tune_fuse - 1 : 0;
+      if (team == 0) {
+        int a = (int)grid, b = p->num_kv_heads;
+        while (b != 0) {
+          const int t = a % b;
+          a = b;
+          b = t;
+        }
+        team = a;
+      }
+      if (team > grid || p->num_kv_heads % team != 0) return PA_ERR_UNSUPPORTED;
+      grid -= grid % team;
+      k.team_size = team;
+    }
+    plan->grid = (int)grid;
     return PA_OK;
   }
 
@@ -368,7 +386,7 @@ int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
   // reduce) drains; the kernel waits (griddepcontrol.wait) before it reads or writes global memory.
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)plan.grid);
-  cfg.blockDim = dim3(FUSE ? pa::tc::kThreadsFused : pa::tc::kThreads);
+  cfg.blockDim = dim3(pa::tc::kThreads);
   cfg.dynamicSmemBytes = (size_t)plan.smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

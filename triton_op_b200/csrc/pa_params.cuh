@@ -64,6 +64,7 @@ struct KernelParams {
   int32_t num_vstages;         // V ring depth (tcgen05 kernel)
   int32_t num_row_blocks;      // ceil(eqG / rows per work item) (tcgen05 kernel)
   int32_t early_start;         // build the partition index before the dependency wait (checked after it)
+  int32_t team_size;           // single-launch form: CTAs per team (divides Hkv and the grid)
 };
 
 // Fixed head of the shared-memory carve: mbarriers and the scan scratch.

@@ -68,13 +68,9 @@ constexpr int kMaxSlots = 4;
 // further ahead than the 32 KB K slots allow).
 constexpr int kQSlots = 4;
 constexpr int kWarpMma = 4 * kNG, kWarpK = 4 * kNG + 1, kWarpV = 4 * kNG + 2, kWarpQ = 4 * kNG + 3;
-// The single-launch form (FUSE) has four more warps, which merge the partitions of a (sequence,
-// kv head) once all of them are stored; see the merge warps in the kernel.  (Twenty warps leave
-// the same register budget per thread as seventeen: five warps on a scheduler either way.)
-constexpr int kWarpMerge = 4 * kNG + 4;
-constexpr int kMergeWarps = 4;
-constexpr int kThreadsFused = kThreads + 32 * kMergeWarps;
-constexpr uint32_t kMergePolls = 1u << 23;   // idle polls of a merge warp (each with a 64-200 ns sleep: about a second)
+// Single-launch form (FUSE): polls of a softmax group that waits for the other partitions of a
+// (sequence, kv head) before it merges them (each with a 64 ns sleep: about a second in all).
+constexpr uint32_t kSetPolls = 1u << 23;
 
 // ---- geometry that depends on the rows per work item (QR = 4, 8 or 16) ---------------------------
 // Row q of the item sits in tile row / TMEM column q (hi half) and QR + q (lo half).
@@ -127,11 +123,9 @@ enum : int {
 // reads is double buffered by the item's parity inside the group.
 constexpr int kOffBars = 0;
 constexpr int kOffTmemPtr = 384;
-constexpr int kOffDone = 388;                     // [3 groups] ints: warps of the group that have stored an item (4 per item)
+constexpr int kOffDone = 388;                     // [3 groups] ints (single-launch form): warps of the group that have stored an item (4 per item)
 constexpr int kOffScan = 400;                     // 32 ints
 constexpr int kOffRowLim = 528;                   // [64] ints: L - 1 - (row / G) for every query row
-constexpr int kOffSetsReady = 784;                // int: sets of this CTA found complete by the polling merge warp
-constexpr int kOffRowsMerged = 788;               // int: merge warps that have finished a set (4 per set)
 constexpr int kOffRedMax = 1024;                  // [4 groups][16 q][4 warps] floats
 constexpr int kOffRedSum = 2048;                  // [4 groups][2 parities][16 q][4 warps] floats
 constexpr int kOffMFin = 4096;                    // [4 groups][2 parities][16] floats (max, log2 domain)
@@ -243,6 +237,67 @@ struct RangeCursor {
     it.head = head;
     it.rb = rb;
     it.part = part;
+    it.ctx = seq_ctx[seq];
+    it.tok0 = it.part * kItemTokens;
+    it.ntok = min(kItemTokens, it.ctx - it.tok0);
+    return it;
+  }
+};
+
+// The numbering of the single-launch form (one row block per item).  The grid is made of teams of
+// p.team_size CTAs.  A team takes a contiguous range of (sequence, partition) rows; its member a
+// takes the kv heads a * hpc .. a * hpc + hpc - 1 of every row (hpc = Hkv / team size), row by
+// row.  So a CTA walks down the partitions of hpc (sequence, kv head) sets at a time and holds
+// all partitions of most of its sets, which is what lets it merge them itself; the heads of a
+// page are still read by the members of a team at about the same time.
+struct TeamRange {
+  int row0, rows, head0, hpc;
+};
+__device__ __forceinline__ TeamRange team_range(const KernelParams& p, int n_sp) {
+  TeamRange t;
+  const int team = (int)blockIdx.x / p.team_size, member = (int)blockIdx.x - team * p.team_size;
+  const int n_teams = (int)gridDim.x / p.team_size;    // the host makes the grid a multiple of the team size
+  const int per = n_sp / n_teams, extra = n_sp - per * n_teams;
+  t.row0 = team * per + min(team, extra);
+  t.rows = per + (team < extra ? 1 : 0);
+  t.hpc = p.Hkv / p.team_size;
+  t.head0 = member * t.hpc;
+  return t;
+}
+struct TeamCursor {
+  int row, hl, seq, head0, hpc, step_row, step_h;
+  // k, step: item numbers inside the CTA
+  __device__ __noinline__ void init(int k, int step, const KernelParams& p, const int* seq_off) {
+    const TeamRange t = team_range(p, seq_off[p.S]);
+    head0 = t.head0;
+    hpc = t.hpc;
+    const int kr = k / hpc;
+    row = t.row0 + kr;
+    hl = k - kr * hpc;
+    step_row = step / hpc;
+    step_h = step - step_row * hpc;
+    int lo = 0, hi = p.S;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (seq_off[mid] <= row) lo = mid; else hi = mid;
+    }
+    seq = lo;
+  }
+  __device__ __forceinline__ void advance(const KernelParams& p, const int* seq_off) {
+    hl += step_h;
+    if (hl >= hpc) {
+      hl -= hpc;
+      ++row;
+    }
+    row += step_row;
+    while (seq < p.S - 1 && seq_off[seq + 1] <= row) ++seq;
+  }
+  __device__ __forceinline__ TcItem item(const KernelParams& p, const int* seq_off, const int* seq_ctx) const {
+    TcItem it;
+    it.seq = seq;
+    it.head = head0 + hl;
+    it.rb = 0;
+    it.part = row - seq_off[seq];
     it.ctx = seq_ctx[seq];
     it.tok0 = it.part * kItemTokens;
     it.ntok = min(kItemTokens, it.ctx - it.tok0);
@@ -382,10 +437,14 @@ struct Geo {
 // ALIBI: add slope[head] * (key position - (context - 1)) to the logits
 // (pa_decode_triton_gluon_fp8.py:905-908).
 // FUSE: the launch also does the cross-partition reduce (paged_attention_decode_v2_reduce_kernel,
-// pa_decode_triton_gluon_fp8.py:1187-1333): four more warps count the finished items of every
-// (sequence, kv head) in p.merge_counters and merge a row set when its last partition is stored.
+// pa_decode_triton_gluon_fp8.py:1187-1333).  CTAs take their items in the TeamCursor numbering, so
+// that a CTA computes all partitions of most of its (sequence, kv head) sets; the softmax group
+// that stores the last of a set's partitions in the CTA merges the set right there (see the
+// epilogue).  A set cut by the end of a team's range is merged by the CTA that holds its first
+// partitions -- it reaches them at the very end of its range -- and the CTAs of the later teams,
+// which meet their share at the start of theirs, hand it over through p.merge_counters.
 template <int BS, int QR, bool PER_TOKEN, bool TRACE, bool ALIBI = false, bool FUSE = false>
-__global__ void __launch_bounds__(FUSE ? kThreadsFused : kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap vmap) {
   using G = Geo<BS>;
   static_assert(!FUSE || (QR <= 8 && !ALIBI && !TRACE), "the single-launch form exists for 4- and 8-row items");
@@ -438,8 +497,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     fence_proxy_async();
     if (FUSE) {
       for (int g = 0; g < NG; ++g) *reinterpret_cast<volatile int*>(smem + kOffDone + 4 * g) = 0;
-      *reinterpret_cast<volatile int*>(smem + kOffSetsReady) = 0;
-      *reinterpret_cast<volatile int*>(smem + kOffRowsMerged) = 0;
     }
   }
   // row r = t * G + g of a kv head sees token j iff j < ctx - (L - 1 - t)
@@ -487,13 +544,17 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       }
     }
   }
-  // items of this CTA: a contiguous range for 16-row items, else every gridDim.x-th item
+  // items of this CTA: a contiguous range for 16-row items, a team's share in the single-launch
+  // form (numbered inside the CTA), else every gridDim.x-th item
   constexpr bool kContiguous = QR == 16;
-  using Cursor = typename std::conditional<kContiguous, RangeCursor, ItemCursor>::type;
+  using Cursor = typename std::conditional<FUSE, TeamCursor,
+                                           typename std::conditional<kContiguous, RangeCursor, ItemCursor>::type>::type;
   const int per_cta = n_items / (int)gridDim.x, extra = n_items - per_cta * (int)gridDim.x;
-  const int first = kContiguous ? (int)blockIdx.x * per_cta + min((int)blockIdx.x, extra) : (int)blockIdx.x;
-  const int stride = kContiguous ? 1 : (int)gridDim.x;
-  const int n_local = per_cta + ((int)blockIdx.x < extra ? 1 : 0);
+  TeamRange team{};
+  if (FUSE) team = team_range(p, n_sp);
+  const int first = FUSE ? 0 : (kContiguous ? (int)blockIdx.x * per_cta + min((int)blockIdx.x, extra) : (int)blockIdx.x);
+  const int stride = (FUSE || kContiguous) ? 1 : (int)gridDim.x;
+  const int n_local = FUSE ? team.rows * team.hpc : per_cta + ((int)blockIdx.x < extra ? 1 : 0);
   bool dead = false;
 
   // Tuning aid: when p.trace is set, lane 0 of each role of CTA 0 stamps the SM clock at a few
@@ -804,115 +865,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(kBarQFull, slot));
       stamp(2, i, 2);
-    }
-  } else if (FUSE && warp >= kWarpMerge) {
-    // ------------------------------------------------------------------ merge warps (single-launch form)
-    // Four warps that turn the launch into the whole decode.
-    //  * Counting (warp mw = 0).  It walks the CTA's items in order; when the softmax group of an
-    //    item has stored its partition (the group's four warps have counted themselves into
-    //    done[group]) it fences once -- which makes those stores, ordered before the fence by the
-    //    counter's release / acquire, visible to the whole GPU -- and adds one to the global counter
-    //    of the item's (sequence, kv head).  Finished items are taken in batches (lane j the j-th of
-    //    them), so a fence is paid per batch, not per item.
-    //  * Merging (all four).  The (sequence, kv head) sets are dealt to the CTAs round-robin by set
-    //    index, whoever computed their partitions: a statically dealt merge cannot pile up on the
-    //    CTAs that happen to run late, which "the last partition's CTA merges" does (a late CTA is
-    //    last for every set it touches).  Warp mw = 1 polls the counter of the CTA's next set; when
-    //    it equals the set's partition count it fences and publishes the set to the other three
-    //    through shared memory, each warp merges the rows r = mw, mw + 4 (one memory round trip per
-    //    row), and the polling warp clears the counter for the next launch once all four are done.
-    // Nothing in the pipeline ever waits for these warps; every poll of theirs is bounded.
-    if constexpr (FUSE) {
-      const int mw = warp - kWarpMerge;
-      const int n_sets = p.S * p.Hkv;
-      const uint32_t sets_ready = sbase + kOffSetsReady, rows_merged = sbase + kOffRowsMerged;
-      ItemCursor cur;
-      if (mw == 0 && n_local > 0) cur.init(first, stride, p, seq_off);
-      int i = mw == 0 ? 0 : n_local;          // next own item to count (counting warp only)
-      int j = (int)blockIdx.x;                // next set this CTA merges
-      int k = 0;                              // sets of this CTA merged so far by this warp
-      uint32_t idle = 0;
-      auto skip_empty = [&]() {
-        while (j < n_sets && seq_off[j / p.Hkv + 1] == seq_off[j / p.Hkv]) j += (int)gridDim.x;
-      };
-      skip_empty();
-      while ((i < n_local || j < n_sets) && !dead) {
-        bool progress = false;
-        if (i < n_local) {
-          const int idx = i + lane;
-          bool ok = false;
-          if (idx < n_local)
-            ok = ld_acquire_cta_shared(sbase + kOffDone + 4 * (idx % NG)) >= 4u * (uint32_t)(idx / NG + 1);
-          const unsigned mask = __ballot_sync(kFullMask, ok);
-          const int ready = mask == kFullMask ? 32 : __ffs((int)~mask) - 1;    // leading run of finished items
-          if (ready > 0) {
-            int my_set = 0;
-            for (int q = 0; q < ready; ++q) {
-              if (lane == q) my_set = cur.seq * p.Hkv + cur.head;
-              cur.advance(p, seq_off);
-            }
-            __threadfence();
-            if (lane < ready) atomicAdd(p.merge_counters + my_set, 1);
-            i += ready;
-            progress = true;
-          }
-        }
-        if (j < n_sets) {
-          const int seq = j / p.Hkv, head = j - seq * p.Hkv;
-          const int np = seq_off[seq + 1] - seq_off[seq];
-          bool go;
-          if (mw == 1) {
-            go = ld_relaxed_gpu(p.merge_counters + j) == np;
-            if (go) {
-              __threadfence();   // the partitions counted into the set are visible from here on
-              __syncwarp();
-              if (lane == 0) st_release_cta_shared(sets_ready, (uint32_t)(k + 1));
-            }
-          } else {
-            go = ld_acquire_cta_shared(sets_ready) > (uint32_t)k;
-          }
-          if (go) {
-            for (int r = mw; r < p.eqG; r += 4) {
-              const int64_t ws_row = (int64_t)seq * p.ws_stride_seq + (int64_t)head * p.ws_stride_head + r;
-              const int64_t tmp_row = (int64_t)seq * p.tmp_stride_seq + (int64_t)head * p.tmp_stride_head +
-                                      (int64_t)r * p.tmp_stride_row + 4 * lane;
-              const bool has_sink = p.sink != nullptr;
-              const float sink_logit = has_sink ? __ldg(p.sink + head * p.G + r % p.G) : 0.f;
-              merge_row_one_chunk(p.max_logits, p.exp_sums, p.tmp_out, ws_row, p.ws_stride_part, tmp_row, p.tmp_stride_part,
-                                  np, sink_logit, has_sink,
-                                  p.out + 2 * ((int64_t)seq * p.out_stride_seq + ((int64_t)head * p.eqG + r) * p.out_stride_head),
-                                  lane);
-            }
-            ++k;
-            __syncwarp();
-            if (lane == 0) red_release_cta_add(rows_merged, 1u);
-            if (mw == 1) {   // all four warps have read the set: clear its counter for the next launch
-              bool all = false;
-              for (uint32_t w = 0; w < kMergePolls && !all; ++w) {
-                all = ld_acquire_cta_shared(rows_merged) >= 4u * (uint32_t)k;
-                if (!all) __nanosleep(64);
-              }
-              if (!all) {
-                fail();
-                break;
-              }
-              if (lane == 0) p.merge_counters[j] = 0;
-            }
-            j += (int)gridDim.x;
-            skip_empty();
-            progress = true;
-          }
-        }
-        if (progress) {
-          idle = 0;
-        } else {
-          if (++idle > kMergePolls) {
-            fail();
-            break;
-          }
-          __nanosleep(mw == 0 ? 64 : 200);
-        }
-      }
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issue
@@ -1274,6 +1226,69 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       return true;
     };
 
+    // Single-launch form.  Item j of this group was the last partition of the set (it.seq, it.head)
+    // that this CTA computes; the set's partitions are the rows [set_row0, set_end) of the index.
+    //  * All of the CTA's earlier items are waited for first: the other two groups count the
+    //    items they have stored (release), and an item of a set precedes the set's later ones.
+    //  * A set that began in an earlier team belongs to the CTA that holds its first partition:
+    //    one thread fences -- which makes this CTA's partitions, ordered before the fence by the
+    //    counts, visible to the whole GPU -- and adds their number to the set's counter.
+    //  * Otherwise this group merges the set, warp w the rows w and w + 4 (the arithmetic of
+    //    pa_reduce_kernel<1>), after the counter has reached the number of partitions that later
+    //    teams compute, if any.  Those teams meet the set at the START of their ranges and this
+    //    CTA at the END of its own, so normally the count is complete long before it is looked at;
+    //    a set longer than a team's range ends with the chain fence - count - poll - merge.
+    //    The counter is cleared for the next launch.
+    // Nobody waits for a group that merges, except through the pipeline's own barriers: the rings
+    // absorb the microsecond or so.  Every poll is bounded.
+    auto finish_set = [&](int j, const TcItem& it, int set_row0, int set_end) -> bool {
+      auto poll = [&](auto&& ready) -> bool {
+        bool ok = false;
+        for (uint32_t w = 0; w < kSetPolls && !ok; ++w) {
+          ok = ready();
+          if (!ok) __nanosleep(64);
+        }
+        return __all_sync(kFullMask, ok);
+      };
+      named_barrier_sync(bar_b, 128);   // the four warps of this group have stored the item
+      for (int g2 = 0; g2 < NG; ++g2) {
+        if (g2 == grp) continue;
+        const uint32_t before = j > g2 ? (uint32_t)((j - g2 + NG - 1) / NG) : 0u;   // items below j of that group
+        const uint32_t at = sbase + kOffDone + 4 * g2;
+        if (!poll([&]() { return ld_acquire_cta_shared(at) >= 4u * before; })) return false;
+      }
+      const int np = set_end - set_row0;
+      const int own = set_row0 + it.part + 1 - max(set_row0, team.row0);   // partitions of the set computed here
+      int32_t* counter = p.merge_counters + (it.seq * p.Hkv + it.head);
+      if (set_row0 < team.row0) {
+        if (wq == 0 && lane == 0) {
+          __threadfence();
+          atomicAdd(counter, own);
+        }
+        return true;
+      }
+      if (own < np) {
+        if (!poll([&]() { return ld_relaxed_gpu(counter) == np - own; })) return false;
+        __threadfence();   // the partitions counted into the set are visible from here on
+      }
+      for (int row = wq; row < p.eqG; row += 4) {
+        const int64_t ws_row = (int64_t)it.seq * p.ws_stride_seq + (int64_t)it.head * p.ws_stride_head + row;
+        const int64_t tmp_row = (int64_t)it.seq * p.tmp_stride_seq + (int64_t)it.head * p.tmp_stride_head +
+                                (int64_t)row * p.tmp_stride_row + 4 * lane;
+        const bool has_sink = p.sink != nullptr;
+        const float sink_logit = has_sink ? __ldg(p.sink + it.head * p.G + row % p.G) : 0.f;
+        merge_row_one_chunk(p.max_logits, p.exp_sums, p.tmp_out, ws_row, p.ws_stride_part, tmp_row, p.tmp_stride_part,
+                            np, sink_logit, has_sink,
+                            p.out + 2 * ((int64_t)it.seq * p.out_stride_seq + ((int64_t)it.head * p.eqG + row) * p.out_stride_head),
+                            lane);
+      }
+      if (own < np) {   // every warp of the group has seen the count: clear it
+        named_barrier_sync(bar_b, 128);
+        if (wq == 0 && lane == 0) *counter = 0;
+      }
+      return true;
+    };
+
     // `tail`: no softmax of a later item of this group ran in between, so the row sums of item j
     // still need a barrier of their own to be visible to the whole group.
     auto epilogue = [&](int j, const TcItem& it, bool tail) -> bool {
@@ -1328,11 +1343,15 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (wq == 0) stamp(7, j, 2 * ch + 1);
       }
       fence_before_sync();  // the O^T loads are ordered before this warp's next arrival on the P barrier
-      if (FUSE) {
-        // this warp's stores of the item are issued: tell the merge warp (a release at CTA scope; the
-        // merge warp's fence makes the stores visible to the GPU, off this group's path)
+      if constexpr (FUSE) {
+        // this warp's stores of the item are issued: count it (a release at CTA scope)
         __syncwarp();
         if (lane == 0) red_release_cta_add(sbase + kOffDone + 4 * grp, 1u);
+        // Was this the last partition of its (sequence, kv head) that this CTA computes -- the
+        // set's last partition, or the one in the last row of the team's range?
+        const int set_row0 = seq_off[it.seq], set_end = seq_off[it.seq + 1];
+        const int row = set_row0 + it.part;
+        if ((row + 1 == set_end || row + 1 == team.row0 + team.rows) && !finish_set(j, it, set_row0, set_end)) return false;
       }
       if (wq == 0) stamp(5, j, 2);
       return true;

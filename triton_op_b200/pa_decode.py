@@ -452,11 +452,12 @@ def paged_attention_decode(
     as 256-token sub-partitions unless the caller passed workspaces of its own.
 
     ``tune={"fuse": 1}`` runs the call as ONE launch where the shape allows it (e4m3fn KV, 256-token
-    partitions, at most 8 query rows per kv head, at most 32 partitions, no ALiBi): four extra
-    warps of the partition kernel merge the partitions of a (sequence, kv head) once the last of
-    them is stored, instead of the reference's second launch (pa_decode_triton_gluon_fp8.py:
-    1862-1887).  Bit-identical to the default two-launch form, and measured slower than it (the
-    last rows wait for two GPU-scope fences and a counter's round trip), so it is opt-in.
+    partitions, at most 8 query rows per kv head, at most 32 partitions, no ALiBi): work items are
+    numbered so that a CTA computes all partitions of most (sequence, kv head) sets and merges
+    them itself, instead of the reference's second launch (pa_decode_triton_gluon_fp8.py:
+    1862-1887); ``1 + T`` asks for teams of T CTAs per (sequence, partition) row.  Bit-identical
+    to the default two-launch form, and measured slower than it (that numbering reads the cache
+    slower than the round-robin one, by more than the second launch costs), so it is opt-in.
     """
     p, keep = build_params(output, query, key_cache, value_cache, sequence_lengths, block_tables,
                            softmax_scale, query_sequence_length, max_sequence_length, compute_type,
