@@ -126,7 +126,10 @@ typedef struct PaDecodeParams {
   int32_t block_size;          /* bs: 16, 64 or 1024 */
   int32_t num_blocks;          /* NB */
   int32_t max_blocks_per_seq;  /* columns of block_tables */
-  int32_t partition_size;      /* tokens per split-KV partition: 256 (reference constant) or 512 */
+  int32_t partition_size;      /* tokens per split-KV partition of the workspaces: 256 (reference constant), or 512
+                                * (e4m3fn KV, L*G <= 16, no ALiBi: the tcgen05 kernel, two 256-token work items per
+                                * partition merged in shared memory), or a multiple of 32 up to 512 with 16-token pages
+                                * (the mma.sync kernel; also what tune_warps = 4 / 8 asks for) */
   int32_t max_partitions;      /* P, the partition extent of the workspaces */
 
   /* strides, in ELEMENTS of the tensor's dtype */

@@ -59,30 +59,99 @@ def test_partition_intermediates(name):
         assert torch.allclose(os_, orr, atol=6e-3, rtol=8e-3)
 
 
-def test_partition512_on_caller_workspaces_keeps_their_layout():
-    """Workspaces passed by the caller are filled at the partition size asked for (the mma.sync kernel)."""
+def _check_partials(cpu, res_ws, psize, what):
+    """exp_sums / max_logits / tmp_output of a run against the exact-fp32 split-KV statement."""
     from oracle import pa_oracle
-    cpu = golden_inputs("partition512")
     c = cpu.cfg
     ks, vs = cpu.flat_scales()
     m_ref, l_ref, o_ref = pa_oracle.split_kv_partials(cpu.query, cpu.key_cache, cpu.value_cache, cpu.block_tables,
-                                                      cpu.context_lens, c.query_len, cpu.softmax_scale, 512, ks, vs)
+                                                      cpu.context_lens, c.query_len, cpu.softmax_scale, psize, ks, vs)
+    es, ml, tmp = (t.cpu() for t in res_ws)
+    for s in range(c.num_seqs):
+        np_s = (int(cpu.context_lens[s]) + psize - 1) // psize
+        live = l_ref[s, :, :np_s] > 0
+        assert torch.equal(torch.isinf(ml[s, :, :np_s]), ~live), what
+        assert torch.allclose(ml[s, :, :np_s][live], m_ref[s, :, :np_s][live], atol=1e-4, rtol=1e-5), what
+        assert torch.allclose(es[s, :, :np_s], l_ref[s, :, :np_s], atol=1e-4, rtol=2e-4), what
+        assert torch.allclose(tmp[s, :, :np_s].float(), o_ref[s, :, :np_s], atol=6e-3, rtol=8e-3), what
+
+
+def _caller_workspaces(inp, psize, fill=float("nan")):
+    c = inp.cfg
+    P = (inp.max_context + psize - 1) // psize
+    shape = (c.num_seqs, c.kv_heads, P, c.q_heads // c.kv_heads * c.query_len)
+    es = torch.full(shape, fill, dtype=torch.float32, device=DEV)
+    ml = torch.full(shape, fill, dtype=torch.float32, device=DEV)
+    tmp = torch.full(shape + (c.head_size,), fill, dtype=torch.bfloat16, device=DEV)
+    return es, ml, tmp
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma.sync"])
+def test_partition512_on_caller_workspaces_keeps_their_layout(kernel):
+    """Workspaces passed by the caller are filled at the partition size asked for: by the tcgen05
+    kernel (two 256-token work items per partition, merged in the second one's epilogue), or by the
+    mma.sync kernel when tune warps asks for it."""
+    from triton_op_b200.pa_decode import query_launch
+    cpu = golden_inputs("partition512")
+    c = cpu.cfg
     inp = cpu.to(DEV)
-    P = (inp.max_context + 511) // 512
-    eqg = c.q_heads // c.kv_heads * c.query_len
-    shape = (c.num_seqs, c.kv_heads, P, eqg)
-    es = torch.zeros(shape, dtype=torch.float32, device=DEV)
-    ml = torch.zeros(shape, dtype=torch.float32, device=DEV)
-    tmp = torch.zeros(shape + (c.head_size,), dtype=torch.bfloat16, device=DEV)
-    got, res = run_operator(inp, exp_sums=es, max_logits=ml, tmp_output=tmp)
+    tune = None if kernel == "tcgen05" else {"warps": 8}
+    es, ml, tmp = _caller_workspaces(inp, 512)
+    launch = query_launch(torch.empty_like(inp.query), inp.query, inp.key_cache, inp.value_cache, inp.context_lens,
+                          inp.block_tables, inp.softmax_scale, c.query_len, inp.max_context, torch.bfloat16, None,
+                          inp.key_scale, inp.value_scale, partition_size=512, exp_sums=es, max_logits=ml,
+                          tmp_output=tmp, tune=tune)
+    assert launch["cta_threads"] == (512 if kernel == "tcgen05" else 256)
+    st = _status()
+    got, res = run_operator(inp, exp_sums=es, max_logits=ml, tmp_output=tmp, status=st, tune=tune)
     torch.cuda.synchronize()
+    assert int(st.item()) == 0
     assert res["partition_size"] == 512
     assert_close(got, oracle_output(cpu), what="partition 512, caller workspaces")
-    for s in range(c.num_seqs):
-        np_s = (int(cpu.context_lens[s]) + 511) // 512
-        live = l_ref[s, :, :np_s] > 0
-        assert torch.allclose(ml[s, :, :np_s].cpu()[live], m_ref[s, :, :np_s][live], atol=1e-4, rtol=1e-5)
-        assert torch.allclose(es[s, :, :np_s].cpu(), l_ref[s, :, :np_s], atol=1e-4, rtol=2e-4)
+    _check_partials(cpu, (es, ml, tmp), 512, f"partition 512 on the {kernel} kernel")
+
+
+@pytest.mark.parametrize("shape", [
+    # (seqs, q heads, kv heads, block, L, context spec, quant)
+    (11, 32, 8, 16, 1, ("cycle", [1, 255, 256, 257, 511, 512, 513, 767, 768, 769, 1300]), "per_tensor"),
+    (9, 16, 2, 16, 1, ("uniform", 1, 6000), "per_token"),
+    (6, 8, 1, 64, 2, ("uniform", 200, 5000), "per_tensor"),
+    (4, 8, 2, 1024, 4, ("uniform", 900, 7000), "per_token"),
+    (3, 16, 1, 16, 1, ("uniform", 3000, 9000), "per_tensor"),       # 16 rows per item
+    (200, 8, 2, 16, 1, ("uniform", 1, 1100), "per_tensor"),         # many sequences, most partitions single or short
+    (2, 8, 1, 16, 1, ("fixed", 40000), "per_tensor"),               # long: a CTA holds many pairs
+])
+def test_partition512_pairs_on_the_tensor_cores(shape):
+    """The PAIR form against the exact split-KV statement at partition 512: contexts that end in
+    the first or the second half of a partition or exactly on a boundary, all page sizes, MTP,
+    per-token scales, 4 / 8 / 16 rows per item; workspaces start as NaN and a second call gives the
+    same bits; the mma.sync kernel's result (16-token pages only) agrees within the tolerance."""
+    from triton_op_b200.inputs import DecodeConfig, make_inputs
+    S, hq, hkv, bs, L, ctx, quant = shape
+    cfg = DecodeConfig("pair", S, hq, hkv, bs, L, ctx, quant=quant, partition_size=512)
+    cpu = make_inputs(cfg, seed=S * 7 + bs, device="cpu")
+    if S >= 9:
+        cpu.context_lens[S // 2] = 0
+    inp = cpu.to(DEV)
+    es, ml, tmp = _caller_workspaces(inp, 512)
+    st = _status()
+    got, res = run_operator(inp, exp_sums=es, max_logits=ml, tmp_output=tmp, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and res["partition_size"] == 512
+    assert_close(got, oracle_output(cpu), what=f"pairs {shape}")
+    if S * inp.max_context <= 120000:
+        _check_partials(cpu, (es, ml, tmp), 512, f"pairs {shape}")
+    first = (got.clone(), es.clone(), ml.clone(), tmp.clone())
+    got2, _ = run_operator(inp, exp_sums=es, max_logits=ml, tmp_output=tmp, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert torch.equal(got2.view(torch.int16), first[0].view(torch.int16))
+    live = ~torch.isnan(first[1])      # entries past a sequence's last partition are never written
+    assert torch.equal(es[live], first[1][live]) and torch.equal(ml[live], first[2][live])
+    if bs == 16:
+        es2, ml2, tmp2 = _caller_workspaces(inp, 512)
+        ref, _ = run_operator(inp, exp_sums=es2, max_logits=ml2, tmp_output=tmp2, tune={"warps": 8})
+        assert_close(got, ref, what=f"pairs {shape}: tcgen05 against mma.sync")
 
 
 def test_workspaces_need_no_clearing_and_runs_are_bit_identical():

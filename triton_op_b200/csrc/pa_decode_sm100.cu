@@ -104,6 +104,7 @@ struct LaunchPlan {
   bool per_token = false;
   bool tensor_path = false;  // tcgen05 kernel (else the mma.sync kernel)
   bool fused = false;        // tcgen05 kernel in its single-launch form: it also merges the partitions
+  bool pair = false;         // tcgen05 kernel on 512-token partitions (two work items per partition)
   bool bf16_kv = false;      // bf16 KV cache (mma.sync bf16 kernel)
   int rows = 0;              // query rows per work item (tcgen05 kernel)
   int grid = 0;
@@ -165,7 +166,11 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
   if (eqG > 64) return PA_ERR_UNSUPPORTED;
   // tcgen05 kernel: 256-token partitions.  tune_warps == 4 / 8 explicitly asks for the mma.sync
   // kernel, which also covers other partition sizes for 16-token pages and up to 16 query rows.
-  const bool tensor_path = !bf16_kv && p->partition_size == pa::tc::kItemTokens && p->tune_warps == 0;
+  // 512-token partitions run on it too (as pairs of 256-token items merged in the epilogue) with
+  // up to 16 query rows and no ALiBi.
+  const bool pair = !bf16_kv && p->partition_size == 2 * pa::tc::kItemTokens && p->tune_warps == 0 && eqG <= 16 &&
+                    p->alibi_slopes == nullptr && p->trace == nullptr;
+  const bool tensor_path = !bf16_kv && (p->partition_size == pa::tc::kItemTokens || pair) && p->tune_warps == 0;
   if (!tensor_path) {
     if (p->block_size != 16 || eqG > 16 || q_item != 2) return PA_ERR_UNSUPPORTED;
     if (p->partition_size % (bf16_kv ? pa::kPageTokens : pa::kStageTokens) != 0 ||
@@ -262,7 +267,8 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
     plan->warps = pa::tc::kThreads / 32;
     // Single launch: one row block per (partition, head), every row's partitions within one chunk
     // of the merge (32), and a counter array for the row sets that are cut by the end of a team's range.
-    plan->fused = allow_fuse && p->merge_counters != nullptr && p->out != nullptr && nrb == 1 && qr <= 8 &&
+    plan->pair = pair;
+    plan->fused = allow_fuse && !pair && p->merge_counters != nullptr && p->out != nullptr && nrb == 1 && qr <= 8 &&
                   p->max_partitions <= 32 && p->alibi_slopes == nullptr && p->trace == nullptr && p->tune_fuse > 0;
     if (plan->fused) {
       k.out = static_cast<uint8_t*>(p->out);
@@ -289,10 +295,13 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
       if (p->tune_stages > 0 && d[0] > p->tune_stages) continue;
       if (p->tune_vstages > 0 && d[1] != p->tune_vstages) continue;
       const int off_p = round_up(off + pa::tc::kQSlots * qslot, 128);
-      const int ring = round_up(off_p + pa::tc::kNG * pa::tc::p_tile_bytes(qr), 1024);
+      const int off_stash = round_up(off_p + pa::tc::kNG * pa::tc::p_tile_bytes(qr), 16);
+      const int stash = pair ? (2 * (qr * pa::kD + 32) + pa::tc::kNG * 2 * 16) * 4 : 0;
+      const int ring = round_up(off_stash + stash, 1024);
       const int total = ring + (d[0] + d[1]) * pa::tc::kHalfSlot;
       if (total <= dev->max_smem_optin) {
         k.off_p = off_p;
+        k.off_stash = off_stash;
         k.off_ring = ring;
         k.off_vring = ring + d[0] * pa::tc::kHalfSlot;
         k.num_stages = d[0];
@@ -303,7 +312,7 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
       }
     }
     if (!placed) return PA_ERR_TOO_LARGE;  // num_seqs too large for the in-kernel index
-    int64_t items = items_cap * nrb;
+    int64_t items = items_cap * nrb * (pair ? 2 : 1);
     int64_t grid = items < dev->sm_count ? items : dev->sm_count;
     if (p->tune_ctas > 0 && p->tune_ctas < grid) grid = p->tune_ctas;
     if (grid < 1) grid = 1;
@@ -376,9 +385,9 @@ int launch_partition_t(const LaunchPlan& plan, cudaStream_t stream) {
   return PA_OK;
 }
 
-template <int BS, int QR, bool PT, bool TRACE, bool ALIBI = false, bool FUSE = false>
+template <int BS, int QR, bool PT, bool TRACE, bool ALIBI = false, bool FUSE = false, bool PAIR = false>
 int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
-  auto kern = pa::tc::pa_partition_fp8_tc_kernel<BS, QR, PT, TRACE, ALIBI, FUSE>;
+  auto kern = pa::tc::pa_partition_fp8_tc_kernel<BS, QR, PT, TRACE, ALIBI, FUSE, PAIR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
   if (e != cudaSuccess) return cuda_fail(e);
   // Programmatic dependent launch: in a decode loop the CTAs may become resident and set up their
@@ -410,6 +419,14 @@ int launch_tensor_bs(const LaunchPlan& plan, cudaStream_t stream) {
     if (plan.rows == 8)
       return pt ? launch_tensor_t<BS, 8, true, false, false, true>(plan, stream) : launch_tensor_t<BS, 8, false, false, false, true>(plan, stream);
     return PA_ERR_UNSUPPORTED;
+  }
+  if (!TRACE && plan.pair) {                  // 512-token partitions
+    switch (plan.rows) {
+      case 4: return pt ? launch_tensor_t<BS, 4, true, false, false, false, true>(plan, stream) : launch_tensor_t<BS, 4, false, false, false, false, true>(plan, stream);
+      case 8: return pt ? launch_tensor_t<BS, 8, true, false, false, false, true>(plan, stream) : launch_tensor_t<BS, 8, false, false, false, false, true>(plan, stream);
+      case 16: return pt ? launch_tensor_t<BS, 16, true, false, false, false, true>(plan, stream) : launch_tensor_t<BS, 16, false, false, false, false, true>(plan, stream);
+      default: return PA_ERR_UNSUPPORTED;
+    }
   }
   if (!TRACE && plan.kp.alibi != nullptr) {   // the ALiBi instantiations
     switch (plan.rows) {

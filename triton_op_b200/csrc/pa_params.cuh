@@ -65,6 +65,7 @@ struct KernelParams {
   int32_t num_row_blocks;      // ceil(eqG / rows per work item) (tcgen05 kernel)
   int32_t early_start;         // build the partition index before the dependency wait (checked after it)
   int32_t team_size;           // single-launch form: CTAs per team (divides Hkv and the grid)
+  int32_t off_stash;           // PAIR form of the tcgen05 kernel: where a partition's first half waits for its second
 };
 
 // Fixed head of the shared-memory carve: mbarriers and the scan scratch.

@@ -126,6 +126,7 @@ constexpr int kOffTmemPtr = 384;
 constexpr int kOffDone = 388;                     // [3 groups] ints (single-launch form): warps of the group that have stored an item (4 per item)
 constexpr int kOffScan = 400;                     // 32 ints
 constexpr int kOffRowLim = 528;                   // [64] ints: L - 1 - (row / G) for every query row
+constexpr int kOffSingles = 784;                  // int (PAIR form): this CTA's units that have one item only
 constexpr int kOffRedMax = 1024;                  // [4 groups][16 q][4 warps] floats
 constexpr int kOffRedSum = 2048;                  // [4 groups][2 parities][16 q][4 warps] floats
 constexpr int kOffMFin = 4096;                    // [4 groups][2 parities][16] floats (max, log2 domain)
@@ -138,8 +139,10 @@ constexpr int kHeadBytes = 5248;
 struct TcItem {
   int seq, head, part, rb;
   int ctx;      // context length of the sequence (clamped)
-  int tok0;     // first token of the partition
-  int ntok;     // tokens of the partition that exist (1..256)
+  int tok0;     // first token of the item
+  int ntok;     // tokens of the item that exist (1..256)
+  int sub;      // PAIR form: which 256-token half of its 512-token partition the item is (else 0)
+  bool paired;  // PAIR form: the partition has both halves
 };
 
 // Walks the work items of one role: item k = first, first + step, ...  Items are numbered
@@ -147,7 +150,7 @@ struct TcItem {
 // needs a search in the partition prefix sum; the cursor does that once and then steps forward.
 struct ItemCursor {
   int sp, head, rb, seq, step_sp, step_head, step_rb;   // (the step is kept in the same mixed radix: no divisions per item)
-  __device__ __noinline__ void init(int k, int step, const KernelParams& p, const int* seq_off) {
+  __device__ __noinline__ void init(int k, int step, const KernelParams& p, const int* seq_off, const int*) {
     const int nrb = p.num_row_blocks, hr_count = p.Hkv * nrb;
     sp = k / hr_count;
     const int hr = k - sp * hr_count;
@@ -187,6 +190,8 @@ struct ItemCursor {
     it.ctx = seq_ctx[seq];
     it.tok0 = it.part * kItemTokens;
     it.ntok = min(kItemTokens, it.ctx - it.tok0);
+    it.sub = 0;
+    it.paired = false;
     return it;
   }
 };
@@ -200,7 +205,7 @@ struct ItemCursor {
 // contiguous form is for 16-row items, where building the query tile is what limits a CTA.)
 struct RangeCursor {
   int seq, head, part, rb, parts, step;
-  __device__ __noinline__ void init(int k, int step_, const KernelParams& p, const int* seq_off) {
+  __device__ __noinline__ void init(int k, int step_, const KernelParams& p, const int* seq_off, const int*) {
     step = step_;
     const int nrb = p.num_row_blocks;
     const int kk = k / nrb;                 // (sequence, head, partition) index
@@ -240,6 +245,8 @@ struct RangeCursor {
     it.ctx = seq_ctx[seq];
     it.tok0 = it.part * kItemTokens;
     it.ntok = min(kItemTokens, it.ctx - it.tok0);
+    it.sub = 0;
+    it.paired = false;
     return it;
   }
 };
@@ -267,7 +274,7 @@ __device__ __forceinline__ TeamRange team_range(const KernelParams& p, int n_sp)
 struct TeamCursor {
   int row, hl, seq, head0, hpc, step_row, step_h;
   // k, step: item numbers inside the CTA
-  __device__ __noinline__ void init(int k, int step, const KernelParams& p, const int* seq_off) {
+  __device__ __noinline__ void init(int k, int step, const KernelParams& p, const int* seq_off, const int*) {
     const TeamRange t = team_range(p, seq_off[p.S]);
     head0 = t.head0;
     hpc = t.hpc;
@@ -300,6 +307,67 @@ struct TeamCursor {
     it.part = row - seq_off[seq];
     it.ctx = seq_ctx[seq];
     it.tok0 = it.part * kItemTokens;
+    it.ntok = min(kItemTokens, it.ctx - it.tok0);
+    it.sub = 0;
+    it.paired = false;
+    return it;
+  }
+};
+
+// The numbering of the PAIR form (512-token partitions in the workspaces, one row block).  The index
+// counts 512-token rows; a unit is (row, kv head) with the head fastest, units are dealt to the
+// CTAs round-robin, and a unit is one work item, or two consecutive ones when the row's second
+// 256 tokens exist -- so both halves of a partition run in one CTA, one right after the other.
+struct PairCursor {
+  int row, head, seq, sub, step_items, step_row, step_head;
+  const int* ctx;
+  __device__ __forceinline__ bool second(const int* seq_off) const {
+    return (row - seq_off[seq]) * (2 * kItemTokens) + kItemTokens < ctx[seq];
+  }
+  __device__ __forceinline__ void next(const KernelParams& p, const int* seq_off) {
+    if (sub == 0 && second(seq_off)) {
+      sub = 1;
+      return;
+    }
+    sub = 0;
+    head += step_head;
+    if (head >= p.Hkv) {
+      head -= p.Hkv;
+      ++row;
+    }
+    row += step_row;
+    while (seq < p.S - 1 && seq_off[seq + 1] <= row) ++seq;
+  }
+  // k, step: item numbers inside the CTA
+  __device__ __noinline__ void init(int k, int step, const KernelParams& p, const int* seq_off, const int* seq_ctx) {
+    ctx = seq_ctx;
+    step_items = step;
+    row = (int)blockIdx.x / p.Hkv;
+    head = (int)blockIdx.x - row * p.Hkv;
+    step_row = (int)gridDim.x / p.Hkv;
+    step_head = (int)gridDim.x - step_row * p.Hkv;
+    sub = 0;
+    int lo = 0, hi = p.S;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (seq_off[mid] <= row) lo = mid; else hi = mid;
+    }
+    seq = lo;
+    for (int j = 0; j < k; ++j) next(p, seq_off);
+  }
+  __device__ __forceinline__ void advance(const KernelParams& p, const int* seq_off) {
+    for (int j = 0; j < step_items; ++j) next(p, seq_off);
+  }
+  __device__ __forceinline__ TcItem item(const KernelParams& p, const int* seq_off, const int* seq_ctx) const {
+    TcItem it;
+    it.seq = seq;
+    it.head = head;
+    it.rb = 0;
+    it.part = row - seq_off[seq];
+    it.ctx = seq_ctx[seq];
+    it.sub = sub;
+    it.paired = sub != 0 || second(seq_off);
+    it.tok0 = it.part * (2 * kItemTokens) + sub * kItemTokens;
     it.ntok = min(kItemTokens, it.ctx - it.tok0);
     return it;
   }
@@ -443,11 +511,16 @@ struct Geo {
 // epilogue).  A set cut by the end of a team's range is merged by the CTA that holds its first
 // partitions -- it reaches them at the very end of its range -- and the CTAs of the later teams,
 // which meet their share at the start of theirs, hand it over through p.merge_counters.
-template <int BS, int QR, bool PER_TOKEN, bool TRACE, bool ALIBI = false, bool FUSE = false>
+// PAIR: the workspaces hold 512-token partitions (p.partition_size = 512, one row block).  The
+// kernel still works on 256-token items; the two halves of a partition run as consecutive items
+// of one CTA (PairCursor), the first half leaves its (max, sum, output) in shared memory and the
+// second half's epilogue merges the two and stores the partition (see the epilogue).
+template <int BS, int QR, bool PER_TOKEN, bool TRACE, bool ALIBI = false, bool FUSE = false, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads, 1)
 pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap vmap) {
   using G = Geo<BS>;
   static_assert(!FUSE || (QR <= 8 && !ALIBI && !TRACE), "the single-launch form exists for 4- and 8-row items");
+  static_assert(!PAIR || (!FUSE && !ALIBI && !TRACE), "the PAIR form is plain");
   constexpr int NG = kNG;
   constexpr bool kSum = sums_in_tensor_core(QR);   // hi and lo products summed by the tensor core
   constexpr int N = acc_n(QR);                 // MMA N and TMEM columns per tile
@@ -455,7 +528,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   constexpr int kQTile = q_tile_bytes(QR);
   constexpr int kPTile = p_tile_bytes(QR);
   constexpr int kPStep = p_step_bytes(QR);
-  constexpr int kPagesPerItem = BS >= kItemTokens ? 1 : kItemTokens / BS;
   extern __shared__ __align__(1024) uint8_t smem[];
   const long long t_entry = TRACE ? clock64() : 0;
   const int tid = threadIdx.x;
@@ -495,8 +567,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     }
     mbar_fence_init();
     fence_proxy_async();
-    if (FUSE) {
+    if (FUSE || PAIR) {
       for (int g = 0; g < NG; ++g) *reinterpret_cast<volatile int*>(smem + kOffDone + 4 * g) = 0;
+      *reinterpret_cast<volatile int*>(smem + kOffSingles) = 0;
     }
   }
   // row r = t * G + g of a kv head sees token j iff j < ctx - (L - 1 - t)
@@ -525,6 +598,17 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   const long long t_dep = TRACE ? clock64() : 0;
   if (!early || !partition_index_still_valid(p, seq_ctx))
     n_sp = build_partition_index(p, seq_off, seq_ctx, reinterpret_cast<int*>(smem + kOffScan));
+  if (PAIR) {
+    // units of this CTA whose row has no second half: the last row of a sequence that ends in its first 256 tokens
+    for (int s = tid; s < p.S; s += (int)blockDim.x) {
+      const int rows = seq_off[s + 1] - seq_off[s];
+      if (rows == 0 || (rows - 1) * (2 * kItemTokens) + kItemTokens < seq_ctx[s]) continue;
+      const int u0 = (seq_off[s + 1] - 1) * p.Hkv;     // the row's units: u0 .. u0 + Hkv - 1
+      int mine = 0;
+      for (int h = 0; h < p.Hkv; ++h) mine += ((u0 + h) % (int)gridDim.x == (int)blockIdx.x) ? 1 : 0;
+      if (mine) atomicAdd(reinterpret_cast<int*>(smem + kOffSingles), mine);
+    }
+  }
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
@@ -547,14 +631,17 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   // items of this CTA: a contiguous range for 16-row items, a team's share in the single-launch
   // form (numbered inside the CTA), else every gridDim.x-th item
   constexpr bool kContiguous = QR == 16;
-  using Cursor = typename std::conditional<FUSE, TeamCursor,
-                                           typename std::conditional<kContiguous, RangeCursor, ItemCursor>::type>::type;
+  using Cursor = typename std::conditional<PAIR, PairCursor, typename std::conditional<FUSE, TeamCursor,
+                                           typename std::conditional<kContiguous, RangeCursor, ItemCursor>::type>::type>::type;
+  // (PAIR form: n_items counts units here, and a unit is one item or two)
   const int per_cta = n_items / (int)gridDim.x, extra = n_items - per_cta * (int)gridDim.x;
   TeamRange team{};
   if (FUSE) team = team_range(p, n_sp);
-  const int first = FUSE ? 0 : (kContiguous ? (int)blockIdx.x * per_cta + min((int)blockIdx.x, extra) : (int)blockIdx.x);
-  const int stride = (FUSE || kContiguous) ? 1 : (int)gridDim.x;
-  const int n_local = FUSE ? team.rows * team.hpc : per_cta + ((int)blockIdx.x < extra ? 1 : 0);
+  const int first = (FUSE || PAIR) ? 0 : (kContiguous ? (int)blockIdx.x * per_cta + min((int)blockIdx.x, extra) : (int)blockIdx.x);
+  const int stride = (FUSE || PAIR || kContiguous) ? 1 : (int)gridDim.x;
+  const int n_units = per_cta + ((int)blockIdx.x < extra ? 1 : 0);
+  const int n_local = FUSE ? team.rows * team.hpc
+                           : (PAIR ? 2 * n_units - *reinterpret_cast<volatile int*>(smem + kOffSingles) : n_units);
   bool dead = false;
 
   // Tuning aid: when p.trace is set, lane 0 of each role of CTA 0 stamps the SM clock at a few
@@ -580,7 +667,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   // fetch it an item ahead and must not touch the value before they use it (a comparison right
   // after the load would make them wait for it there), so clamping is a separate step.
   auto page_id_raw = [&](const TcItem& it, int pg) -> int {
-    const int64_t col = BS >= kItemTokens ? (int64_t)(it.tok0 / BS) : (int64_t)it.part * kPagesPerItem + pg;
+    const int64_t col = BS >= kItemTokens ? (int64_t)(it.tok0 / BS) : (int64_t)(it.tok0 / BS + pg);
     return __ldg(p.block_tables + (int64_t)it.seq * p.bt_stride_seq + col);
   };
   auto clamp_page = [&](int id, bool report) -> int {
@@ -618,7 +705,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     TcItem it_next{};
     int pid_next = 0;
     if (n_local > 0) {
-      cur.init(first, stride, p, seq_off);
+      cur.init(first, stride, p, seq_off, seq_ctx);
       it_next = cur.item(p, seq_off, seq_ctx);
       pid_next = load_page_id(it_next);
     }
@@ -733,7 +820,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     };
     bool fresh_next = true;
     if (n_local > 0) {
-      cur.init(first, stride, p, seq_off);
+      cur.init(first, stride, p, seq_off, seq_ctx);
       it_next = cur.item(p, seq_off, seq_ctx);
       load_q(it_next, q_next);
     }
@@ -1291,12 +1378,44 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
 
     // `tail`: no softmax of a later item of this group ran in between, so the row sums of item j
     // still need a barrier of their own to be visible to the whole group.
+    // PAIR form: waits (bounded) until every item of this CTA below `limit` has been stored or
+    // stashed by its group (the groups count their finished epilogues, release / acquire)
+    auto items_below_done = [&](int limit) -> bool {
+      for (int g2 = 0; g2 < NG; ++g2) {
+        if (g2 == grp) continue;   // this group's own earlier items are behind it in program order
+        const uint32_t before = limit > g2 ? (uint32_t)((limit - g2 + NG - 1) / NG) : 0u;
+        const uint32_t at = sbase + kOffDone + 4 * g2;
+        bool ok = false;
+        for (uint32_t w = 0; w < kSetPolls && !ok; ++w) {
+          ok = ld_acquire_cta_shared(at) >= 4u * before;
+          if (!ok) __nanosleep(32);
+        }
+        if (!__all_sync(kFullMask, ok)) return false;
+      }
+      return true;
+    };
+    // PAIR form: where the first half of a partition leaves its result for the second half.  Two
+    // buffers, taken by the first half's item number: [QR rows][128 dims] fp32 outputs (value scale
+    // applied, not yet divided by the row sum), then per row the maximum (base-2 domain) and the sum
+    // (units of 1/256); behind the buffers, per group and parity, the first half's weight per row.
+    float* stash = reinterpret_cast<float*>(smem + p.off_stash);
+    constexpr int kStashFloats = QR * kD + 2 * 16;
+    float* g_first = stash + 2 * kStashFloats;   // [groups][2 parities][16]
+
     auto epilogue = [&](int j, const TcItem& it, bool tail) -> bool {
       const uint32_t gu = (uint32_t)(j / NG);
       const int par = grp * 2 + (int)(gu & 1);
       const float* rs = red_sum + par * 64;
+      // PAIR form: 0 = a partition of one item, 1 = first half (stash), 2 = second half (merge and store)
+      const int half = !PAIR || !it.paired ? 0 : 1 + it.sub;
+      float* st = stash + (((half == 2 ? j - 1 : j) >> 1) & 1) * kStashFloats;
       if (tail) named_barrier_sync(bar_b, 128);
       if (wq == 0) stamp(5, j, 0);
+      if (PAIR && half != 0) {
+        // second half: the first half (item j - 1, another group's) must be stashed.  First half: the
+        // buffer's previous reader is item j - 2 at the latest (see the buffer choice above).
+        if (!items_below_done(half == 2 ? j : j - 1)) return false;
+      }
       if (!wait(bar(kBarOFull, par), (gu >> 1) & 1)) return false;
       if (wq == 0) stamp(5, j, 1);
       fence_after_sync();
@@ -1307,12 +1426,33 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       if (r < QR) {
         const float4 l4 = *reinterpret_cast<const float4*>(rs + r * 4);
         const float lsum = (l4.x + l4.y) + (l4.z + l4.w);   // in units of 1/256
-        f_row[par * 16 + r] = lsum > 0.f ? __fdividef(vfin, lsum) : 0.f;
-        if (r < rows) {
-          const int64_t ws = (int64_t)it.seq * p.ws_stride_seq + (int64_t)it.head * p.ws_stride_head +
-                             (int64_t)it.part * p.ws_stride_part + it.rb * QR + r;
-          p.max_logits[ws] = m_fin[par * 16 + r] * kLn2;
-          p.exp_sums[ws] = lsum * (1.0f / 256.0f);
+        const int64_t ws = (int64_t)it.seq * p.ws_stride_seq + (int64_t)it.head * p.ws_stride_head +
+                           (int64_t)it.part * p.ws_stride_part + it.rb * QR + r;
+        if (PAIR && half == 1) {
+          f_row[par * 16 + r] = vfin;
+          st[QR * kD + r] = m_fin[par * 16 + r];
+          st[QR * kD + 16 + r] = lsum;
+        } else if (PAIR && half == 2) {
+          // log-sum-exp merge of the two halves (pa_decode_triton_gluon_fp8.py:1187-1333 does the
+          // same across partitions): weights relative to the common maximum
+          const float m_a = st[QR * kD + r], l_a = st[QR * kD + 16 + r], m_b = m_fin[par * 16 + r];
+          const float m = fmaxf(m_a, m_b);
+          const float e_a = (l_a > 0.f && m_a > -INFINITY) ? ex2(m_a - m) : 0.f;
+          const float e_b = (lsum > 0.f && m_b > -INFINITY) ? ex2(m_b - m) : 0.f;
+          const float l = l_a * e_a + lsum * e_b;
+          const float inv = l > 0.f ? __fdividef(1.0f, l) : 0.f;
+          g_first[par * 16 + r] = e_a * inv;
+          f_row[par * 16 + r] = vfin * e_b * inv;
+          if (r < rows) {
+            p.max_logits[ws] = m * kLn2;
+            p.exp_sums[ws] = l * (1.0f / 256.0f);
+          }
+        } else {
+          f_row[par * 16 + r] = lsum > 0.f ? __fdividef(vfin, lsum) : 0.f;
+          if (r < rows) {
+            p.max_logits[ws] = m_fin[par * 16 + r] * kLn2;
+            p.exp_sums[ws] = lsum * (1.0f / 256.0f);
+          }
         }
       }
       named_barrier_sync(bar_b, 128);
@@ -1336,13 +1476,23 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (wq == 0) stamp(7, j, 2 * ch);
 #pragma unroll
         for (int q = 0; q < RC; ++q) {
-          const float o = row_value(h, l, q) * f[q];
-          if (ch * RC + q < rows) *dst = (unsigned short)(pack_bf16x2(o, 0.f) & 0xffffu);
+          float o = row_value(h, l, q) * f[q];
+          if (PAIR && half == 1) {          // thread r keeps its head dim of every row for the second half
+            st[(ch * RC + q) * kD + r] = o;
+          } else {
+            if (PAIR && half == 2) o = fmaf(st[(ch * RC + q) * kD + r], g_first[par * 16 + ch * RC + q], o);
+            if (ch * RC + q < rows) *dst = (unsigned short)(pack_bf16x2(o, 0.f) & 0xffffu);
+          }
           dst += row_stride;
         }
         if (wq == 0) stamp(7, j, 2 * ch + 1);
       }
       fence_before_sync();  // the O^T loads are ordered before this warp's next arrival on the P barrier
+      if constexpr (PAIR) {
+        // this warp's part of the item is stored or stashed (and what it read of the stash is read): count it
+        __syncwarp();
+        if (lane == 0) red_release_cta_add(sbase + kOffDone + 4 * grp, 1u);
+      }
       if constexpr (FUSE) {
         // this warp's stores of the item are issued: count it (a release at CTA scope)
         __syncwarp();
@@ -1360,7 +1510,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     // group g walks the CTA's items g, g+NG, ...; the epilogue of an item runs after the softmax
     // of the group's next item, by which time its P.V product has long been issued
     Cursor cur;
-    if (grp < n_local) cur.init(first + grp * stride, NG * stride, p, seq_off);
+    if (grp < n_local) cur.init(first + grp * stride, NG * stride, p, seq_off, seq_ctx);
     // the group's current item and the two after it (for the scale prefetch)
     TcItem it0{}, it1{}, it2{};
     int pid1[2] = {0, 0};            // block-table entries of it1's pages, in flight
