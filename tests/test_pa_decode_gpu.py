@@ -325,8 +325,11 @@ def test_single_launch_decode_with_sets_cut_in_many_places(shape):
     assert int(get_merge_counters(res["temporary_output"], S, hkv).abs().sum().item()) == 0
 
 
-def test_lengths_and_tables_written_by_the_kernel_just_before_the_call():
-    """The tcgen05 kernel builds its partition index before its dependency wait and checks it after.
+@pytest.mark.parametrize("form", ["two launches", "single launch", "partition 512"])
+def test_lengths_and_tables_written_by_the_kernel_just_before_the_call(form):
+    """The tcgen05 kernel builds its partition index before its dependency wait and checks it after
+    (in all its forms: the team ranges of the single-launch form and the item counts of the
+    512-token form are derived from the index that passed the check).
     Here the kernel right before every call in the stream rewrites the context lengths and the block
     tables (what a serving loop's bookkeeping kernel does), alternating between two batches, with a
     long decode call before it so that the next call's CTAs are resident early: every result must be
@@ -353,18 +356,30 @@ def test_lengths_and_tables_written_by_the_kernel_just_before_the_call():
     torch.cuda.synchronize()
     st = _status()
     outs = []
+    kw = {}
+    if form == "single launch":
+        kw = {"tune": {"fuse": 1}}
+    if form == "partition 512":
+        P = (max_ctx + 511) // 512
+        kw = {"partition_size": 512,
+              "exp_sums": torch.zeros((48, 8, P, 4), dtype=torch.float32, device=DEV),
+              "max_logits": torch.zeros((48, 8, P, 4), dtype=torch.float32, device=DEV),
+              "tmp_output": torch.zeros((48, 8, P, 4, 128), dtype=torch.bfloat16, device=DEV)}
     for it in range(40):
         v = (it * 7 + it // 3) % 2
         out = torch.empty_like(a.query)
         cur_lens.copy_(lens[v])            # kernels in the same stream, directly before the call
         cur_tables.copy_(tables[v])
         paged_attention_decode(out, a.query, kc, vc, cur_lens, cur_tables, a.softmax_scale, 1, max_ctx, torch.bfloat16, None,
-                               a.key_scale, a.value_scale, status=st)
+                               a.key_scale, a.value_scale, status=st, **kw)
         outs.append((v, out))
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     for v, out in outs:
-        assert torch.equal(out.view(torch.int16), want[v].view(torch.int16))
+        if form == "partition 512":     # another split: the same attention within the tolerance
+            assert_close(out, want[v], what="partition 512 after rewritten lengths")
+        else:
+            assert torch.equal(out.view(torch.int16), want[v].view(torch.int16))
 
 
 def test_zero_length_sequences_and_empty_batch():
