@@ -296,7 +296,7 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
       if (p->tune_vstages > 0 && d[1] != p->tune_vstages) continue;
       const int off_p = round_up(off + pa::tc::kQSlots * qslot, 128);
       const int off_stash = round_up(off_p + pa::tc::kNG * pa::tc::p_tile_bytes(qr), 16);
-      const int stash = pair ? (2 * (qr * pa::kD + 32) + pa::tc::kNG * 2 * 16) * 4 : 0;
+      const int stash = pair ? 2 * (qr * pa::kD * 2 + 2 * 16 * 4) + pa::tc::kNG * 2 * 16 * 4 : 0;
       const int ring = round_up(off_stash + stash, 1024);
       const int total = ring + (d[0] + d[1]) * pa::tc::kHalfSlot;
       if (total <= dev->max_smem_optin) {

@@ -1395,12 +1395,13 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       return true;
     };
     // PAIR form: where the first half of a partition leaves its result for the second half.  Two
-    // buffers, taken by the first half's item number: [QR rows][128 dims] fp32 outputs (value scale
-    // applied, not yet divided by the row sum), then per row the maximum (base-2 domain) and the sum
-    // (units of 1/256); behind the buffers, per group and parity, the first half's weight per row.
-    float* stash = reinterpret_cast<float*>(smem + p.off_stash);
-    constexpr int kStashFloats = QR * kD + 2 * 16;
-    float* g_first = stash + 2 * kStashFloats;   // [groups][2 parities][16]
+    // buffers, taken by the first half's item number: [QR rows][128 dims] bf16 outputs (what the
+    // partition would hold in the workspace if it ended there), then per row the maximum (base-2
+    // domain) and the sum (units of 1/256) in fp32; behind the buffers, per group and parity, the
+    // first half's weight per row.  (bf16: with fp32 outputs the buffers would cost 8-row items a
+    // stage of the V ring.)
+    constexpr int kStashBytes = QR * kD * 2 + 2 * 16 * 4;
+    float* g_first = reinterpret_cast<float*>(smem + p.off_stash + 2 * kStashBytes);   // [groups][2 parities][16]
 
     auto epilogue = [&](int j, const TcItem& it, bool tail) -> bool {
       const uint32_t gu = (uint32_t)(j / NG);
@@ -1408,7 +1409,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       const float* rs = red_sum + par * 64;
       // PAIR form: 0 = a partition of one item, 1 = first half (stash), 2 = second half (merge and store)
       const int half = !PAIR || !it.paired ? 0 : 1 + it.sub;
-      float* st = stash + (((half == 2 ? j - 1 : j) >> 1) & 1) * kStashFloats;
+      uint8_t* st_raw = smem + p.off_stash + (((half == 2 ? j - 1 : j) >> 1) & 1) * kStashBytes;
+      unsigned short* st_o = reinterpret_cast<unsigned short*>(st_raw);            // [QR][128] bf16
+      float* st = reinterpret_cast<float*>(st_raw + QR * kD * 2);                  // [16] maxima, [16] sums
       if (tail) named_barrier_sync(bar_b, 128);
       if (wq == 0) stamp(5, j, 0);
       if (PAIR && half != 0) {
@@ -1429,19 +1432,19 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         const int64_t ws = (int64_t)it.seq * p.ws_stride_seq + (int64_t)it.head * p.ws_stride_head +
                            (int64_t)it.part * p.ws_stride_part + it.rb * QR + r;
         if (PAIR && half == 1) {
-          f_row[par * 16 + r] = vfin;
-          st[QR * kD + r] = m_fin[par * 16 + r];
-          st[QR * kD + 16 + r] = lsum;
+          f_row[par * 16 + r] = lsum > 0.f ? __fdividef(vfin, lsum) : 0.f;
+          st[r] = m_fin[par * 16 + r];
+          st[16 + r] = lsum;
         } else if (PAIR && half == 2) {
           // log-sum-exp merge of the two halves (pa_decode_triton_gluon_fp8.py:1187-1333 does the
           // same across partitions): weights relative to the common maximum
-          const float m_a = st[QR * kD + r], l_a = st[QR * kD + 16 + r], m_b = m_fin[par * 16 + r];
+          const float m_a = st[r], l_a = st[16 + r], m_b = m_fin[par * 16 + r];
           const float m = fmaxf(m_a, m_b);
           const float e_a = (l_a > 0.f && m_a > -INFINITY) ? ex2(m_a - m) : 0.f;
           const float e_b = (lsum > 0.f && m_b > -INFINITY) ? ex2(m_b - m) : 0.f;
           const float l = l_a * e_a + lsum * e_b;
           const float inv = l > 0.f ? __fdividef(1.0f, l) : 0.f;
-          g_first[par * 16 + r] = e_a * inv;
+          g_first[par * 16 + r] = l_a * e_a * inv;   // the first half's outputs are already divided by its sum
           f_row[par * 16 + r] = vfin * e_b * inv;
           if (r < rows) {
             p.max_logits[ws] = m * kLn2;
@@ -1478,9 +1481,10 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         for (int q = 0; q < RC; ++q) {
           float o = row_value(h, l, q) * f[q];
           if (PAIR && half == 1) {          // thread r keeps its head dim of every row for the second half
-            st[(ch * RC + q) * kD + r] = o;
+            st_o[(ch * RC + q) * kD + r] = (unsigned short)(pack_bf16x2(o, 0.f) & 0xffffu);
           } else {
-            if (PAIR && half == 2) o = fmaf(st[(ch * RC + q) * kD + r], g_first[par * 16 + ch * RC + q], o);
+            if (PAIR && half == 2)
+              o = fmaf(__uint_as_float((uint32_t)st_o[(ch * RC + q) * kD + r] << 16), g_first[par * 16 + ch * RC + q], o);
             if (ch * RC + q < rows) *dst = (unsigned short)(pack_bf16x2(o, 0.f) & 0xffffu);
           }
           dst += row_stride;
