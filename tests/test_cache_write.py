@@ -105,6 +105,58 @@ def test_cuda_write_is_bit_exact(bs, mode):
         assert torch.equal(sc_d[0].cpu(), sc_ref[0]) and torch.equal(sc_d[1].cpu(), sc_ref[1])
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["per_token", "per_tensor"])
+def test_cuda_write_rounds_ties_and_tiny_values_like_the_oracle(mode):
+    """Inputs made to land on the rounding boundaries: quotients that are exact halfway points
+    between two e4m3 values (ties go to even), quotients in e4m3's subnormal range and below its
+    smallest step, bf16 subnormals, and the largest finite bf16.  Bytes and scales as the oracle's."""
+    from oracle import pa_oracle
+    from triton_op_b200.cache_write import write_kv_cache
+    dev = "cuda:0"
+    nb, hkv, d, bs, T = 40, 2, 128, 16, 600
+    g = torch.Generator().manual_seed(77)
+    halfway = torch.tensor([1.0625, 1.1875, 1.3125, 1.4375, 1.5625, 1.6875, 1.8125, 1.9375])
+
+    def adversarial():
+        sign = torch.where(torch.rand(T, hkv, d, generator=g) < 0.5, -1.0, 1.0)
+        m = halfway[torch.randint(0, 8, (T, hkv, d), generator=g)]
+        e = torch.randint(-12, 8, (T, hkv, d), generator=g).float()
+        x = sign * m * torch.exp2(e)
+        x[:, :, 0] = 448.0 * torch.exp2(torch.randint(-3, 3, (T, hkv), generator=g).float())   # amax: a power-of-two scale
+        x[::7, :, 5] = 1e-39                      # bf16 subnormal
+        x[::11, :, 9] = 2.0 ** -30
+        x[3::13, 0, :] *= 2.0 ** -11              # whole vectors of small quotients
+        x[5, 1, 0] = 3.3895e38                    # largest finite bf16: the scale itself is huge
+        return x.to(torch.bfloat16)
+
+    key, value = adversarial(), adversarial()
+    slots = torch.randperm(nb * bs, generator=g)[:T].to(torch.int64)
+    slots[: 16 * 20] = torch.arange(16 * 20) + 16 * 3          # twenty full runs: the vector-store path too
+    seen = set()
+    keep = [i for i, v in enumerate(slots.tolist()) if not (v in seen or seen.add(v))]
+    slots, key, value = slots[keep], key[keep], value[keep]
+    kc = torch.full((nb, hkv, d // 16, bs, 16), 1.0).to(FP8)
+    vc = torch.full((nb, hkv, d, bs), 1.0).to(FP8)
+    if mode == "per_token":
+        scales = (torch.full((nb, hkv, bs, 1), -1.0), torch.full((nb, hkv, bs, 1), -1.0))
+    else:
+        scales = (torch.tensor(2.0 ** -4), torch.tensor(0.173))
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    sc_ref = tuple(s.clone() for s in scales)
+    pa_oracle.write_kv_cache(key, value, kc_ref, vc_ref, slots, *sc_ref)
+    kc_d, vc_d = kc.to(dev), vc.to(dev)
+    sc_d = tuple(s.to(dev) for s in scales)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    write_kv_cache(key.to(dev), value.to(dev), kc_d, vc_d, slots.to(dev), *sc_d, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(kc_d.cpu().view(torch.uint8), kc_ref.view(torch.uint8))
+    assert torch.equal(vc_d.cpu().view(torch.uint8), vc_ref.view(torch.uint8))
+    if mode == "per_token":
+        assert torch.equal(sc_d[0].cpu(), sc_ref[0]) and torch.equal(sc_d[1].cpu(), sc_ref[1])
+
+
 def _prefill_slots(nb, bs, chunks, g):
     """Slots of token streams that walk pages the way a prefill chunk does: consecutive positions of a
     sequence from a start offset inside its first page, pages taken from a shuffled pool."""
