@@ -202,6 +202,28 @@ def test_garbage_beyond_context_is_ignored():
     assert torch.equal(out.view(torch.int16), base.view(torch.int16))
 
 
+@pytest.mark.parametrize("name", ["gqa4_ragged", "mtp4_g2_pertoken", "bf16_kv"])
+@pytest.mark.parametrize("case", ["peaked", "one-hot", "flat", "underflow", "zero query", "zero keys"])
+def test_extreme_logit_distributions(name, case):
+    """Queries scaled by powers of two from 2^-120 to 2^8 (attention from uniform to one-hot; the
+    query rows' power-of-two pre-scale at both ends of its range), all-zero queries and all-zero
+    keys, against the oracle on the same inputs."""
+    import copy
+    cpu = copy.copy(golden_inputs(name))
+    factor = {"peaked": 2.0 ** 4, "one-hot": 2.0 ** 8, "flat": 2.0 ** -40, "underflow": 2.0 ** -120,
+              "zero query": 0.0, "zero keys": 1.0}[case]
+    cpu.query = (cpu.query.float() * factor).to(torch.bfloat16)
+    cpu.query_tokens = (cpu.query_tokens.float() * factor).to(torch.bfloat16)
+    if case == "zero keys":
+        cpu.key_cache = torch.zeros_like(cpu.key_cache.view(torch.uint8 if cpu.key_cache.element_size() == 1 else torch.int16)).view(cpu.key_cache.dtype)
+    ref = oracle_output(cpu)
+    st = _status()
+    out, _ = run_operator(cpu.to(DEV), status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert_close(out, ref, what=f"{name}, {case}")
+
+
 def test_bad_page_id_and_long_context_are_clamped_and_reported():
     from triton_op_b200 import _lib
     inp = golden_inputs("cfg1_small").to(DEV)
