@@ -282,7 +282,7 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
     k.off_seq_ctx = off + round_up((p->num_seqs + 1) * 4, 16);
     off = round_up(off + index_bytes, 128);
     k.off_q = off;
-    const int qslot = pa::tc::q_slot_bytes(qr, per_token);
+    const int qslot = pa::tc::q_slot_bytes(qr, pa::tc::staged_token_scales(p->block_size, per_token));
     // Ring depths (K ring, V ring), deepest that fits.  The K ring is never shallower than the
     // three softmax groups (P.V trails QK^T by two items in the issue loop, and a group's waits
     // on the ring barriers assume a slot is not refilled within that lag), the V ring never

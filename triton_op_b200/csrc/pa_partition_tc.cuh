@@ -90,8 +90,19 @@ __host__ __device__ constexpr int acc_n(int qr) { return sums_in_tensor_core(qr)
 // counters.
 constexpr int kQHdr = 64;    // offset of the item header behind the tile
 constexpr int kQSlope = 80;  // offset of the tile's 16 ALiBi slopes (base-2 logit domain) behind the tile
-__host__ __device__ constexpr int q_slot_bytes(int qr, bool /*per_token*/) {
-  return q_tile_bytes(qr) + kQSlope + 64;
+// With per-token scales and pages of 64 tokens or more, the item part also holds the item's 256
+// key scales and 256 value scales (2 KB), brought in by bulk copies of the query producer: the
+// scales of a page are contiguous there.  (With 16-token pages they would be 32 copies of 64
+// bytes per item; the softmax threads fetch their own tokens' scales from global memory instead.)
+#ifndef PA_STAGED_SCALES
+#define PA_STAGED_SCALES 1
+#endif
+constexpr int kQTokScales = kQSlope + 64;   // offset of the item's token scales behind the tile
+__host__ __device__ constexpr bool staged_token_scales(int block_size, bool per_token) {
+  return PA_STAGED_SCALES && per_token && block_size >= 64;
+}
+__host__ __device__ constexpr int q_slot_bytes(int qr, bool staged_scales) {
+  return q_tile_bytes(qr) + kQTokScales + (staged_scales ? 2 * kItemTokens * 4 : 0);
 }
 // P^T tile of one item: 8 k-steps x [row blocks of 8][2 K units][8 rows][16 tokens].  The strides
 // are padded off the 128-byte grid (k-step stride = 48 mod 128) so that byte stores of one warp
@@ -524,7 +535,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   constexpr int NG = kNG;
   constexpr bool kSum = sums_in_tensor_core(QR);   // hi and lo products summed by the tensor core
   constexpr int N = acc_n(QR);                 // MMA N and TMEM columns per tile
-  constexpr int kQSlotBytes = q_slot_bytes(QR, PER_TOKEN);
+  constexpr bool kStaged = staged_token_scales(BS, PER_TOKEN);
+  constexpr int kQSlotBytes = q_slot_bytes(QR, kStaged);
   constexpr int kQTile = q_tile_bytes(QR);
   constexpr int kPTile = p_tile_bytes(QR);
   constexpr int kPStep = p_step_bytes(QR);
@@ -819,10 +831,18 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       return it.seq == key_seq && it.head == key_head && ((tile_slots >> (4 * it.rb)) & 8u) != 0;
     };
     bool fresh_next = true;
+    // staged token scales: lane pg copies the scales of page pg of the item (one page of 1024
+    // tokens, or four of 64); its block-table entry is fetched an item ahead
+    constexpr int kScalePages = BS >= kItemTokens ? 1 : kItemTokens / (BS >= 64 ? BS : 64);
+    auto scale_page_id = [&](const TcItem& it) -> int {
+      return (kStaged && lane < kScalePages && lane < pages_of(it)) ? page_id_raw(it, lane) : 0;
+    };
+    int spid_next = 0;
     if (n_local > 0) {
       cur.init(first, stride, p, seq_off, seq_ctx);
       it_next = cur.item(p, seq_off, seq_ctx);
       load_q(it_next, q_next);
+      spid_next = scale_page_id(it_next);
     }
     for (int i = 0; i < n_local && !dead; ++i) {
       const TcItem it = it_next;
@@ -833,6 +853,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         for (int ps = 0; ps < kPasses; ++ps) qraw[ps][e] = q_next[ps][e];
       }
       const bool fresh = fresh_next;
+      const int spid = spid_next;
       if (it.seq != key_seq || it.head != key_head) {
         key_seq = it.seq;
         key_head = it.head;
@@ -864,6 +885,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         it_next = cur.item(p, seq_off, seq_ctx);
         fresh_next = !have_tile(it_next);
         if (fresh_next) load_q(it_next, q_next);
+        spid_next = scale_page_id(it_next);
       }
       const int slot = i % kQSlots;
       const uint32_t use = (uint32_t)(i / kQSlots);
@@ -874,6 +896,22 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       const uint32_t aux = qt + kQTile;                                   // the tile's row scales
       const uint32_t item_aux = q_ring + slot * kQSlotBytes + kQTile;     // the item's header
       if (lane == 0) sts32(item_aux + kQHdr, (uint32_t)tslot);
+      if (kStaged) {
+        // the item's token scales, straight from the scale tensors into the slot; they complete
+        // the slot's barrier together with this warp's arrival below
+        constexpr int kRun = (BS >= kItemTokens ? kItemTokens : BS) * 4;          // bytes of one page's scales inside the item
+        const int npg = pages_of(it);
+        if (lane == 0) mbar_expect_tx(bar(kBarQFull, slot), (uint32_t)(2 * npg * kRun));
+        __syncwarp();
+        if (lane < kScalePages && lane < npg) {
+          const int64_t idx = (int64_t)clamp_page(spid, false) * p.kvs_stride_block + (int64_t)it.head * p.kvs_stride_head +
+                              (BS >= kItemTokens ? it.tok0 % BS : 0);
+          const uint32_t dst = item_aux + kQTokScales + lane * kRun;
+          const uint64_t pol = l2_policy_evict_first();
+          bulk_g2s(dst, p.k_scale + idx, kRun, bar(kBarQFull, slot), pol);
+          bulk_g2s(dst + kItemTokens * 4, p.v_scale + idx, kRun, bar(kBarQFull, slot), pol);
+        }
+      }
       // (rolled: the code of every role's loop should stay resident in the instruction cache)
 #pragma unroll 1
       for (int ps = 0; ps < (fresh ? kPasses : 0); ++ps) {
@@ -1059,7 +1097,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     auto load_tok_pids = [&](const TcItem& it, int (&pid)[2]) {
       pid[0] = 0;
       pid[1] = 0;
-      if (PER_TOKEN) {
+      if (PER_TOKEN && !kStaged) {
         // tokens of one lane share a page unless pages hold 64 tokens (then they are 128 tokens apart)
         if (tok[0] < it.ntok) pid[0] = page_id_raw(it, BS == 16 ? (tok[0] >> 4) : (BS == 64 ? (tok[0] >> 6) : 0));
         if (BS == 64) {
@@ -1072,7 +1110,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     auto load_tok_scales = [&](const TcItem& it, const int (&pid)[2], float (&sc)[4]) {  // k0, k1, v0, v1
 #pragma unroll
       for (int e = 0; e < 4; ++e) sc[e] = 0.f;
-      if (PER_TOKEN) {
+      if (PER_TOKEN && !kStaged) {
 #pragma unroll
         for (int tg = 0; tg < 2; ++tg) {
           if (tok[tg] < it.ntok) {
@@ -1128,7 +1166,13 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       };
       if (NCH == 1) load_row_consts(0);
       float ks_tok[2] = {1.f, 1.f}, vs_tok[2] = {1.f, 1.f};
-      if (PER_TOKEN) {
+      if (kStaged) {        // the item's slot holds its tokens' scales (key scales, then value scales)
+#pragma unroll
+        for (int tg = 0; tg < 2; ++tg) {
+          ks_tok[tg] = __uint_as_float(lds32(item_aux + kQTokScales + tok[tg] * 4));
+          vs_tok[tg] = __uint_as_float(lds32(item_aux + kQTokScales + (kItemTokens + tok[tg]) * 4));
+        }
+      } else if (PER_TOKEN) {
         ks_tok[0] = tok_scales[0], ks_tok[1] = tok_scales[1];
         vs_tok[0] = tok_scales[2], vs_tok[1] = tok_scales[3];
       }
