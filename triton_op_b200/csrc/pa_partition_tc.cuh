@@ -97,7 +97,14 @@ constexpr int kQSlope = 80;  // offset of the tile's 16 ALiBi slopes (base-2 log
 #ifndef PA_STAGED_SCALES
 #define PA_STAGED_SCALES 1
 #endif
-constexpr int kQTokScales = kQSlope + 64;   // offset of the item's token scales behind the tile
+// The item part of a slot also carries the work item itself (32 bytes: the query producer has
+// decoded it anyway), so that the softmax groups need no cursor of their own -- unless they
+// fetch per-token scales themselves and must know their items two ahead.
+#ifndef PA_ITEM_FROM_SLOT
+#define PA_ITEM_FROM_SLOT 1
+#endif
+constexpr int kQItem = kQSlope + 64;        // offset of the item (8 ints) behind the tile
+constexpr int kQTokScales = kQItem + 32;    // offset of the item's token scales behind the tile
 __host__ __device__ constexpr bool staged_token_scales(int block_size, bool per_token) {
   return PA_STAGED_SCALES && per_token && block_size >= 64;
 }
@@ -537,6 +544,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   constexpr int N = acc_n(QR);                 // MMA N and TMEM columns per tile
   constexpr bool kStaged = staged_token_scales(BS, PER_TOKEN);
   constexpr int kQSlotBytes = q_slot_bytes(QR, kStaged);
+  constexpr bool kItemFromSlot = PA_ITEM_FROM_SLOT && (!PER_TOKEN || kStaged);
   constexpr int kQTile = q_tile_bytes(QR);
   constexpr int kPTile = p_tile_bytes(QR);
   constexpr int kPStep = p_step_bytes(QR);
@@ -895,7 +903,14 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       const uint32_t qt = q_ring + tslot * kQSlotBytes;
       const uint32_t aux = qt + kQTile;                                   // the tile's row scales
       const uint32_t item_aux = q_ring + slot * kQSlotBytes + kQTile;     // the item's header
-      if (lane == 0) sts32(item_aux + kQHdr, (uint32_t)tslot);
+      if (lane == 0) {
+        sts32(item_aux + kQHdr, (uint32_t)tslot);
+        if (kItemFromSlot) {
+          sts128(item_aux + kQItem, make_uint4((uint32_t)it.seq, (uint32_t)it.head, (uint32_t)it.part, (uint32_t)it.rb));
+          sts128(item_aux + kQItem + 16, make_uint4((uint32_t)it.ctx, (uint32_t)it.tok0, (uint32_t)it.ntok,
+                                                    (uint32_t)it.sub | (it.paired ? 2u : 0u)));
+        }
+      }
       if (kStaged) {
         // the item's token scales, straight from the scale tensors into the slot; they complete
         // the slot's barrier together with this warp's arrival below
@@ -1124,7 +1139,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       }
     };
 
-    auto softmax = [&](int i, const TcItem& it, const float (&tok_scales)[4]) -> bool {
+    auto softmax = [&](int i, TcItem& it_io, const float (&tok_scales)[4]) -> bool {
       const int slot = i % kQSlots;
       const uint32_t use = (uint32_t)(i / kQSlots), gu = (uint32_t)(i / NG);
       const int par = grp * 2 + (int)(gu & 1);  // double-buffer index of what the epilogue reads
@@ -1136,6 +1151,13 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       if (!wait(bar(kBarQFull, slot), use & 1)) return false;
       const uint32_t item_aux = q_ring + slot * kQSlotBytes + kQTile;   // the item's header
       const uint32_t aux = q_ring + lds32(item_aux + kQHdr) * kQSlotBytes + kQTile;   // the tile's row scales
+      if (kItemFromSlot) {
+        const uint4 a = lds128(item_aux + kQItem), b = lds128(item_aux + kQItem + 16);
+        it_io.seq = (int)a.x, it_io.head = (int)a.y, it_io.part = (int)a.z, it_io.rb = (int)a.w;
+        it_io.ctx = (int)b.x, it_io.tok0 = (int)b.y, it_io.ntok = (int)b.z;
+        it_io.sub = (int)(b.w & 1u), it_io.paired = (b.w & 2u) != 0;
+      }
+      const TcItem& it = it_io;
       // Per-row constants of one chunk of rows (fetched again for every chunk: the chunk loops
       // are rolled): the positive factor that turns a raw product into a base-2 logit, and the
       // causal limit.  The query slot is released when pass 2 has read them for the last time.
@@ -1557,13 +1579,14 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
 
     // group g walks the CTA's items g, g+NG, ...; the epilogue of an item runs after the softmax
     // of the group's next item, by which time its P.V product has long been issued
+    // (With the item in the slot, the softmax fills it0 in and none of the cursor code below exists.)
     Cursor cur;
-    if (grp < n_local) cur.init(first + grp * stride, NG * stride, p, seq_off, seq_ctx);
+    if (!kItemFromSlot && grp < n_local) cur.init(first + grp * stride, NG * stride, p, seq_off, seq_ctx);
     // the group's current item and the two after it (for the scale prefetch)
     TcItem it0{}, it1{}, it2{};
     int pid1[2] = {0, 0};            // block-table entries of it1's pages, in flight
     float sc0[4] = {0.f, 0.f, 0.f, 0.f};   // token scales of it0, in flight
-    if (grp < n_local) {
+    if (!kItemFromSlot && grp < n_local) {
       it0 = cur.item(p, seq_off, seq_ctx);
       if (PER_TOKEN) {
         int pid0[2];
@@ -1571,7 +1594,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         load_tok_scales(it0, pid0, sc0);
       }
     }
-    if (grp + NG < n_local) {
+    if (!kItemFromSlot && grp + NG < n_local) {
       cur.advance(p, seq_off);
       it1 = cur.item(p, seq_off, seq_ctx);
       load_tok_pids(it1, pid1);
@@ -1586,8 +1609,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         float sc_use[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) sc_use[e] = sc0[e];
-        if (PER_TOKEN && i + NG < n_local) load_tok_scales(it1, pid1, sc0);
-        if (i + 2 * NG < n_local) {
+        if (!kItemFromSlot && PER_TOKEN && i + NG < n_local) load_tok_scales(it1, pid1, sc0);
+        if (!kItemFromSlot && i + 2 * NG < n_local) {
           cur.advance(p, seq_off);
           it2 = cur.item(p, seq_off, seq_ctx);
           load_tok_pids(it2, pid1);
@@ -1598,8 +1621,10 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       if (!more) break;
       it_prev = it0;
       prev = i;
-      it0 = it1;
-      it1 = it2;
+      if (!kItemFromSlot) {
+        it0 = it1;
+        it1 = it2;
+      }
     }
   }
 
