@@ -100,6 +100,11 @@ constexpr int kQSlope = 80;  // offset of the tile's 16 ALiBi slopes (base-2 log
 // The item part of a slot also carries the work item itself (32 bytes: the query producer has
 // decoded it anyway), so that the softmax groups need no cursor of their own -- unless they
 // fetch per-token scales themselves and must know their items two ahead.
+// The softmax's exponent offsets are computed once per row by one thread (1) or by every thread
+// from the four warps' maxima (0).
+#ifndef PA_ROW_OFFSETS
+#define PA_ROW_OFFSETS 1
+#endif
 #ifndef PA_ITEM_FROM_SLOT
 #define PA_ITEM_FROM_SLOT 1
 #endif
@@ -145,6 +150,7 @@ constexpr int kOffDone = 388;                     // [3 groups] ints (single-lau
 constexpr int kOffScan = 400;                     // 32 ints
 constexpr int kOffRowLim = 528;                   // [64] ints: L - 1 - (row / G) for every query row
 constexpr int kOffSingles = 784;                  // int (PAIR form): this CTA's units that have one item only
+constexpr int kOffRowOff = 800;                   // [3 groups][16] floats: exponent offset of every row of the group's current item
 constexpr int kOffRedMax = 1024;                  // [4 groups][16 q][4 warps] floats
 constexpr int kOffRedSum = 2048;                  // [4 groups][2 parities][16 q][4 warps] floats
 constexpr int kOffMFin = 4096;                    // [4 groups][2 parities][16] floats (max, log2 domain)
@@ -568,6 +574,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   float* v_max = reinterpret_cast<float*>(smem + kOffVMax);
   float* v_norm = reinterpret_cast<float*>(smem + kOffVNorm);
   float* f_row = reinterpret_cast<float*>(smem + kOffFRow);
+  float* row_off = reinterpret_cast<float*>(smem + kOffRowOff);
   const uint32_t q_ring = sbase + p.off_q;     // kQSlots x kQSlotBytes
   const uint32_t p_tiles = sbase + p.off_p;    // NG x kPTile
   const uint32_t k_ring = sbase + p.off_ring;  // NSK x kHalfSlot
@@ -1253,6 +1260,19 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       }
       if (wq == 0) stamp(6, i, 1);
       named_barrier_sync(bar_a, 128);
+#if PA_ROW_OFFSETS
+      // thread `row` of the group combines the four warps' maxima of its row, once for the group:
+      // the exponent offset every thread applies in pass 2 (raw * factor - m * factor + 8 as one
+      // multiply-add per element), and the row's maximum (base-2 logit domain) for the epilogue
+      if (r < QR) {
+        const float4 m4 = *reinterpret_cast<const float4*>(rm + r * 4);
+        const float m = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w));
+        const float sc = __uint_as_float(lds32(aux + r * 4));
+        row_off[grp * 16 + r] = (m == -INFINITY) ? 8.0f : (ALIBI ? 8.0f - m : fmaf(-m, sc, 8.0f));
+        m_fin[par * 16 + r] = (m == -INFINITY || ALIBI) ? m : m * sc;
+      }
+      named_barrier_sync(bar_a, 128);
+#endif
       float vinv = 1.0f, vnorm = 1.0f;
       if (PER_TOKEN) {
         const float4 vm4 = *reinterpret_cast<const float4*>(v_max + grp * 4);
@@ -1286,18 +1306,31 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (NCH > 1) raw_logits(ch, s_keep);  // recomputed rather than kept: registers
         uint32_t pbytes[2][2 * ((RC + 3) / 4)];  // [tg][hi words, lo words], row q = byte q % 4
         float hi[2][RC], lo[2][RC];
+#if PA_ROW_OFFSETS
+        float offs[RC];
+#pragma unroll
+        for (int q4 = 0; q4 < RC; q4 += 4) {
+          const float4 o4 = *reinterpret_cast<const float4*>(row_off + grp * 16 + ch * RC + q4);
+          offs[q4] = o4.x, offs[q4 + 1] = o4.y, offs[q4 + 2] = o4.z, offs[q4 + 3] = o4.w;
+        }
+#endif
 #pragma unroll
         for (int q = 0; q < RC; ++q) {
+#if PA_ROW_OFFSETS
+          const float off_q = offs[q];
+#else
           const float4 m4 = *reinterpret_cast<const float4*>(rm + (ch * RC + q) * 4);
           const float m = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w));
+          const float off_q = (m == -INFINITY) ? 8.0f : (ALIBI ? 8.0f - m : fmaf(-m, row_scale[q], 8.0f));
+#endif
           // exponent argument raw * factor - m * factor + 8 as one multiply-add per element
           float p0, p1;
           if (ALIBI) {   // s_keep holds finished logits
-            const float off = (m == -INFINITY) ? 8.0f : 8.0f - m;
+            const float off = off_q;
             p0 = ex2(s_keep[0][q] + off);
             p1 = ex2(s_keep[1][q] + off);
           } else {
-            const float off = (m == -INFINITY) ? 8.0f : fmaf(-m, row_scale[q], 8.0f);
+            const float off = off_q;
             p0 = ex2(fmaf(s_keep[0][q], row_scale[q], off));
             p1 = ex2(fmaf(s_keep[1][q], row_scale[q], off));
           }
@@ -1325,7 +1358,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (NCH > 1) row_sums(ch, psum);
       }
       // thread `row` of the group keeps the row's maximum (base-2 logit domain) for the epilogue
-      if (r < QR) {
+      if (!PA_ROW_OFFSETS && r < QR) {
         const float4 m4 = *reinterpret_cast<const float4*>(rm + r * 4);
         const float m = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w));
         const float sc = __uint_as_float(lds32(aux + r * 4));
