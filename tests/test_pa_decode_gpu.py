@@ -503,6 +503,32 @@ def test_reference_matrix_large_batches(batch, bs, hq, hkv, ql, ctx):
     assert torch.equal(out_sub, out[rows])
 
 
+@pytest.mark.parametrize("batch,hq,hkv,ql,bs", [(1500, 16, 1, 1, 64), (1200, 8, 1, 2, 1024), (4500, 4, 1, 1, 64)])
+def test_batches_too_large_for_staged_token_scales(batch, hq, hkv, ql, bs):
+    """With per-token scales and pages of 64 tokens or more the kernel keeps an item's scales in its
+    query slot -- while the in-kernel index of the batch (8 bytes per sequence) leaves room for the
+    2 KB per slot.  These batches do not: the form whose softmax threads fetch the scales runs, and
+    a sample agrees with the oracle and, bit for bit, with its own batch of five (which is staged)."""
+    from triton_op_b200.inputs import DecodeConfig, make_inputs, subset_inputs
+    from triton_op_b200.pa_decode import query_launch
+    cfg = DecodeConfig(f"big{batch}", batch, hq, hkv, bs, ql, ("uniform", 1, 300), quant="per_token")
+    inp = make_inputs(cfg, seed=batch, device=DEV)
+    st = _status()
+    out, _ = run_operator(inp, status=st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and bool(torch.isfinite(out.float()).all())
+    pick = sorted(torch.randperm(batch, generator=torch.Generator().manual_seed(batch))[:5].tolist())
+    sub = subset_inputs(inp, pick)
+    rows = [s * ql + t for s in pick for t in range(ql)]
+    assert_close(out[rows], oracle_output(sub), what=f"{cfg.name}: sampled sequences vs oracle")
+    out_sub, _ = run_operator(sub, status=st)        # the small batch runs the staged form
+    assert torch.equal(out_sub, out[rows])
+    big = query_launch(torch.empty_like(inp.query), inp.query, inp.key_cache, inp.value_cache, inp.context_lens,
+                       inp.block_tables, inp.softmax_scale, ql, inp.max_context, torch.bfloat16, None,
+                       inp.key_scale, inp.value_scale)
+    assert big["ring_stages"] >= 3 and big["smem_bytes"] <= 227 * 1024
+
+
 @pytest.mark.parametrize("name,num_seqs", [("cfg3_llama70b_mtp", 12), ("cfg4_longctx", 3), ("cfg5_serving_fp8", 48),
                                            ("cfg5_serving_bf16", 48)])
 def test_baseline_configs_reduced_batch(name, num_seqs):

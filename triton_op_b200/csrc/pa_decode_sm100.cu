@@ -105,6 +105,7 @@ struct LaunchPlan {
   bool tensor_path = false;  // tcgen05 kernel (else the mma.sync kernel)
   bool fused = false;        // tcgen05 kernel in its single-launch form: it also merges the partitions
   bool pair = false;         // tcgen05 kernel on 512-token partitions (two work items per partition)
+  bool staged = false;       // tcgen05 kernel: per-token scales are staged in the query slots
   bool bf16_kv = false;      // bf16 KV cache (mma.sync bf16 kernel)
   int rows = 0;              // query rows per work item (tcgen05 kernel)
   int grid = 0;
@@ -282,7 +283,11 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
     k.off_seq_ctx = off + round_up((p->num_seqs + 1) * 4, 16);
     off = round_up(off + index_bytes, 128);
     k.off_q = off;
-    const int qslot = pa::tc::q_slot_bytes(qr, pa::tc::staged_token_scales(p->block_size, per_token));
+    // Per-token scales of pages of 64 tokens or more are staged in the query slots (2 KB each)
+    // while that fits; a batch whose index leaves no room runs the form whose softmax threads
+    // fetch the scales themselves.  (The 16-row form for 512-token partitions never stages: its
+    // slots and its halves' buffers do not fit together.)
+    const bool want_staged = pa::tc::staged_token_scales(p->block_size, per_token) && !(pair && qr == 16);
     // Ring depths (K ring, V ring), deepest that fits.  The K ring is never shallower than the
     // three softmax groups (P.V trails QK^T by two items in the issue loop, and a group's waits
     // on the ring barriers assume a slot is not refilled within that lag), the V ring never
@@ -291,6 +296,10 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
     if (p->tune_stages > 0 && p->tune_stages < 3) return PA_ERR_UNSUPPORTED;
     if (p->tune_vstages > 0 && p->tune_vstages < 2) return PA_ERR_UNSUPPORTED;
     bool placed = false;
+    for (int attempt = 0; attempt < 2 && !placed; ++attempt) {
+    const bool staged = want_staged && attempt == 0;
+    if (attempt == 1 && (!want_staged || pair)) break;     // nothing else to try
+    const int qslot = pa::tc::q_slot_bytes(qr, staged);
     for (const auto& d : kDepths) {
       if (p->tune_stages > 0 && d[0] > p->tune_stages) continue;
       if (p->tune_vstages > 0 && d[1] != p->tune_vstages) continue;
@@ -307,11 +316,14 @@ int make_plan(const PaDecodeParams* p, LaunchPlan* plan, bool allow_fuse = false
         k.num_stages = d[0];
         k.num_vstages = d[1];
         plan->smem = total;
+        plan->staged = staged;
         placed = true;
         break;
       }
     }
+    }
     if (!placed) return PA_ERR_TOO_LARGE;  // num_seqs too large for the in-kernel index
+    if (want_staged && !plan->staged) plan->fused = false;   // (the single-launch form exists staged only)
     int64_t items = items_cap * nrb * (pair ? 2 : 1);
     int64_t grid = items < dev->sm_count ? items : dev->sm_count;
     if (p->tune_ctas > 0 && p->tune_ctas < grid) grid = p->tune_ctas;
@@ -385,9 +397,9 @@ int launch_partition_t(const LaunchPlan& plan, cudaStream_t stream) {
   return PA_OK;
 }
 
-template <int BS, int QR, bool PT, bool TRACE, bool ALIBI = false, bool FUSE = false, bool PAIR = false>
+template <int BS, int QR, bool PT, bool TRACE, bool ALIBI = false, bool FUSE = false, bool PAIR = false, bool STAGE = true>
 int launch_tensor_t(const LaunchPlan& plan, cudaStream_t stream) {
-  auto kern = pa::tc::pa_partition_fp8_tc_kernel<BS, QR, PT, TRACE, ALIBI, FUSE, PAIR>;
+  auto kern = pa::tc::pa_partition_fp8_tc_kernel<BS, QR, PT, TRACE, ALIBI, FUSE, PAIR, STAGE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, plan.smem);
   if (e != cudaSuccess) return cuda_fail(e);
   // Programmatic dependent launch: in a decode loop the CTAs may become resident and set up their
@@ -427,6 +439,17 @@ int launch_tensor_bs(const LaunchPlan& plan, cudaStream_t stream) {
       case 16: return pt ? launch_tensor_t<BS, 16, true, false, false, false, true>(plan, stream) : launch_tensor_t<BS, 16, false, false, false, false, true>(plan, stream);
       default: return PA_ERR_UNSUPPORTED;
     }
+  }
+  if constexpr (!TRACE && BS >= 64) {
+  if (pt && !plan.staged && !plan.pair) {     // per-token scales fetched by the softmax threads
+    const bool al = plan.kp.alibi != nullptr;
+    switch (plan.rows) {
+      case 4: return al ? launch_tensor_t<BS, 4, true, false, true, false, false, false>(plan, stream) : launch_tensor_t<BS, 4, true, false, false, false, false, false>(plan, stream);
+      case 8: return al ? launch_tensor_t<BS, 8, true, false, true, false, false, false>(plan, stream) : launch_tensor_t<BS, 8, true, false, false, false, false, false>(plan, stream);
+      case 16: return al ? launch_tensor_t<BS, 16, true, false, true, false, false, false>(plan, stream) : launch_tensor_t<BS, 16, true, false, false, false, false, false>(plan, stream);
+      default: return PA_ERR_UNSUPPORTED;
+    }
+  }
   }
   if (!TRACE && plan.kp.alibi != nullptr) {   // the ALiBi instantiations
     switch (plan.rows) {

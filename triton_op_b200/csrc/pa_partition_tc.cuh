@@ -539,7 +539,9 @@ struct Geo {
 // kernel still works on 256-token items; the two halves of a partition run as consecutive items
 // of one CTA (PairCursor), the first half leaves its (max, sum, output) in shared memory and the
 // second half's epilogue merges the two and stores the partition (see the epilogue).
-template <int BS, int QR, bool PER_TOKEN, bool TRACE, bool ALIBI = false, bool FUSE = false, bool PAIR = false>
+// STAGE: per-token scales of pages of 64 tokens or more travel in the query slots (see q_slot_bytes);
+// false where the host found no room for that.
+template <int BS, int QR, bool PER_TOKEN, bool TRACE, bool ALIBI = false, bool FUSE = false, bool PAIR = false, bool STAGE = true>
 __global__ void __launch_bounds__(kThreads, 1)
 pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_constant__ CUtensorMap vmap) {
   using G = Geo<BS>;
@@ -548,7 +550,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   constexpr int NG = kNG;
   constexpr bool kSum = sums_in_tensor_core(QR);   // hi and lo products summed by the tensor core
   constexpr int N = acc_n(QR);                 // MMA N and TMEM columns per tile
-  constexpr bool kStaged = staged_token_scales(BS, PER_TOKEN);
+  constexpr bool kStaged = STAGE && staged_token_scales(BS, PER_TOKEN) && !(PAIR && QR == 16);
   constexpr int kQSlotBytes = q_slot_bytes(QR, kStaged);
   constexpr bool kItemFromSlot = PA_ITEM_FROM_SLOT && (!PER_TOKEN || kStaged);
   constexpr int kQTile = q_tile_bytes(QR);
