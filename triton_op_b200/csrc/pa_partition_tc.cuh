@@ -119,10 +119,24 @@ __host__ __device__ constexpr int q_slot_bytes(int qr, bool staged_scales) {
 // P^T tile of one item: 8 k-steps x [row blocks of 8][2 K units][8 rows][16 tokens].  The strides
 // are padded off the 128-byte grid (k-step stride = 48 mod 128) so that byte stores of one warp
 // to different K units and k-steps fall into different banks.
+#ifndef PA_P_MN
+#define PA_P_MN 1
+#endif
+#if PA_P_MN
+// P^T as an MN-major operand: the 16 tile rows (N) of one token are 16 consecutive bytes, the
+// tokens (K) of an 8-token core matrix are 16 bytes apart and core matrices follow one another,
+// so token t of the item sits at t * 16 and a softmax thread stores its token's bytes of a
+// chunk of rows with one vector store.  16-row items have a tile for the hi rows and one for the lo rows.
+constexpr int kPLbo = 128;                          // between 8-token core matrices (along K)
+constexpr int kPSbo = 4096;                         // between 16-row blocks (there is one per tile)
+__host__ __device__ constexpr int p_step_bytes(int) { return 512; }                     // a k-step: 32 tokens
+__host__ __device__ constexpr int p_tile_bytes(int qr) { return qr <= 8 ? 4096 : 8192; }
+#else
 constexpr int kPLbo = 144;                          // between the two K units of a k-step
 constexpr int kPSbo = 288;                          // between row blocks
 __host__ __device__ constexpr int p_step_bytes(int qr) { return qr <= 8 ? 560 : 1200; }
 __host__ __device__ constexpr int p_tile_bytes(int qr) { return 8 * p_step_bytes(qr) + 64; }
+#endif
 // TMEM columns of group g start at 4 * N * g: S^T (tg = 0 | 1) then O^T (parity 0 | 1), N each.
 __host__ __device__ constexpr int tmem_cols(int qr) { return 4 * acc_n(qr) * kNG <= 256 ? 256 : 512; }
 
@@ -1018,6 +1032,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issue
     constexpr uint32_t kIdesc = idesc_f32acc(128, N, 0, 0);
+    constexpr uint32_t kIdescPV = idesc_f32acc(128, N, 0, 0, PA_P_MN != 0);   // P^T may be MN-major
     const bool leader = elect_one();  // the one lane that issues every MMA and commit
     // per item i: group g = i % NG, use gu = i / NG of the group's buffers, O^T parity gu & 1.
     // P.V of an item is issued kLag items after its QK^T, so a softmax group has that long to
@@ -1070,8 +1085,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         for (int ks = 0; ks < 8; ++ks) {
           const uint64_t ad = vd + (uint64_t)((v16 ? Geo<16>::v_kstep(ks) : G::v_kstep(ks)) >> 4);
           const uint64_t bd = pd + (uint64_t)((ks * kPStep) >> 4);
-          if (leader) mma_f8_ss(d0, ad, bd, kIdesc, ks > 0);
-          if (kSum && leader) mma_f8_ss(d0, ad, bd + (uint64_t)((QR / 8 * kPSbo) >> 4), kIdesc, true);   // the lo rows' tile
+          if (leader) mma_f8_ss(d0, ad, bd, kIdescPV, ks > 0);
+          if (kSum && leader)   // the lo rows' tile
+            mma_f8_ss(d0, ad, bd + (uint64_t)((PA_P_MN ? 4096 : QR / 8 * kPSbo) >> 4), kIdescPV, true);
         }
         if (leader) mma_commit(bar(kBarOFull, ob));
         __syncwarp();
@@ -1096,7 +1112,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     uint32_t p_at[2];
 #pragma unroll
     for (int tg = 0; tg < 2; ++tg)
-      p_at[tg] = p_tiles + grp * kPTile + (tok[tg] >> 5) * kPStep + ((tok[tg] >> 4) & 1) * kPLbo + (tok[tg] & 15);
+      p_at[tg] = PA_P_MN ? p_tiles + grp * kPTile + tok[tg] * 16
+                         : p_tiles + grp * kPTile + (tok[tg] >> 5) * kPStep + ((tok[tg] >> 4) & 1) * kPLbo + (tok[tg] & 15);
 
     // One chunk of RC rows of a transposed accumulator tile: value = hi column + lo column / 16.
     auto load_rows = [&](uint32_t tile, int ch, uint32_t (&h)[8], uint32_t (&l)[8]) {
@@ -1351,11 +1368,21 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
             pbytes[tg][w] = pack_e4m3x4(hi[tg][4 * w], hi[tg][4 * w + 1], hi[tg][4 * w + 2], hi[tg][4 * w + 3]);
             pbytes[tg][W + w] = pack_e4m3x4(lo[tg][4 * w], lo[tg][4 * w + 1], lo[tg][4 * w + 2], lo[tg][4 * w + 3]);
           }
+#if PA_P_MN
+          // tile row n of the token is byte n of its 16: hi rows at q, lo rows at QR + q (their own tile with 16 rows)
+          if constexpr (RC == 4) {
+            sts64(p_at[tg], pbytes[tg][0], pbytes[tg][1]);
+          } else {
+            sts64(p_at[tg] + ch * 8, pbytes[tg][0], pbytes[tg][1]);
+            sts64(p_at[tg] + (QR == 16 ? 4096 + ch * 8 : 8), pbytes[tg][2], pbytes[tg][3]);
+          }
+#else
 #pragma unroll
           for (int q = 0; q < RC; ++q) {
             sts8(p_at[tg] + hi_at + q * 16, pbytes[tg][q >> 2] >> (8 * (q & 3)));
             sts8(p_at[tg] + lo_at + q * 16, pbytes[tg][W + (q >> 2)] >> (8 * (q & 3)));
           }
+#endif
         }
         if (NCH > 1) row_sums(ch, psum);
       }

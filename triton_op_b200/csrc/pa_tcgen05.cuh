@@ -48,9 +48,9 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int 
 //   bits [4,6)  accumulator format (1 = f32)      bits [7,10) A format     bits [10,13) B format
 //   bit 15 / 16 A / B major (0 = K-major)          bits [17,23) N >> 3      bits [24,29) M >> 4
 // kind::f8f6f4 formats: 0 = e4m3.  kind::f16 formats: 0 = f16, 1 = bf16.
-__host__ __device__ constexpr uint32_t idesc_f32acc(int m, int n, int a_fmt, int b_fmt) {
-  return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(m >> 4) << 24);
+__host__ __device__ constexpr uint32_t idesc_f32acc(int m, int n, int a_fmt, int b_fmt, bool b_mn_major = false) {
+  return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] * B[smem], e4m3 operands, K = 32 per instruction.  One thread issues.
@@ -168,6 +168,9 @@ __device__ __forceinline__ void sts8(uint32_t addr, uint32_t v) {
 }
 __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t lo, uint32_t hi) {
+  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(lo), "r"(hi) : "memory");
 }
 __device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
