@@ -105,6 +105,9 @@ constexpr int kQSlope = 80;  // offset of the tile's 16 ALiBi slopes (base-2 log
 #ifndef PA_ROW_OFFSETS
 #define PA_ROW_OFFSETS 1
 #endif
+#ifndef PA_KEEP_LOGITS
+#define PA_KEEP_LOGITS 1
+#endif
 #ifndef PA_ITEM_FROM_SLOT
 #define PA_ITEM_FROM_SLOT 1
 #endif
@@ -567,6 +570,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   constexpr bool kStaged = STAGE && staged_token_scales(BS, PER_TOKEN) && !(PAIR && QR == 16);
   constexpr int kQSlotBytes = q_slot_bytes(QR, kStaged);
   constexpr bool kItemFromSlot = PA_ITEM_FROM_SLOT && (!PER_TOKEN || kStaged);
+  constexpr bool kKeepInTmem = sums_in_tensor_core(QR);   // two chunks of rows, one accumulator column per row
   constexpr int kQTile = q_tile_bytes(QR);
   constexpr int kPTile = p_tile_bytes(QR);
   constexpr int kPStep = p_step_bytes(QR);
@@ -1262,6 +1266,14 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
 #pragma unroll 1
       for (int ch = 0; ch < NCH; ++ch) {
         raw_logits(ch, s_keep);
+#if PA_KEEP_LOGITS
+        // 16-row items: both chunks do not fit in registers, so the finished (scaled, masked) logits
+        // go back into the accumulator columns they came from, and pass 2 reads them as they are
+        if constexpr (kKeepInTmem) {
+          tmem_st8(tmem_grp + ch * 8, s_keep[0]);
+          tmem_st8(tmem_grp + N + ch * 8, s_keep[1]);
+        }
+#endif
         float mx[RC];
 #pragma unroll
         for (int q = 0; q < RC; ++q) mx[q] = fmaxf(s_keep[0][q], s_keep[1][q]);
@@ -1307,6 +1319,9 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (!wait(bar(kBarOFull, 2 * grp + (int)(pu & 1)), (pu >> 1) & 1)) return false;
       }
 
+#if PA_KEEP_LOGITS
+      if constexpr (kKeepInTmem) tmem_st_wait();
+#endif
       if (wq == 0) stamp(6, i, 2);
       // ---- pass 2: P = exp2(raw * factor - m) * 256, split into hi / lo e4m3, stored as P^T
       // row sums of one chunk: lane ends up with the sum of one row over the warp's 64 tokens
@@ -1322,6 +1337,17 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       float psum[RC];
 #pragma unroll 1
       for (int ch = 0; ch < NCH; ++ch) {
+#if PA_KEEP_LOGITS
+        if constexpr (kKeepInTmem) {
+          uint32_t a[8], b[8];
+          tmem_ld8(tmem_grp + ch * 8, a);
+          tmem_ld8(tmem_grp + N + ch * 8, b);
+          load_row_consts(ch);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < RC; ++q) s_keep[0][q] = __uint_as_float(a[q]), s_keep[1][q] = __uint_as_float(b[q]);
+        } else
+#endif
         if (NCH > 1) raw_logits(ch, s_keep);  // recomputed rather than kept: registers
         uint32_t pbytes[2][2 * ((RC + 3) / 4)];  // [tg][hi words, lo words], row q = byte q % 4
         float hi[2][RC], lo[2][RC];
