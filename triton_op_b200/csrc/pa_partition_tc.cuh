@@ -102,12 +102,6 @@ constexpr int kQSlope = 80;  // offset of the tile's 16 ALiBi slopes (base-2 log
 // fetch per-token scales themselves and must know their items two ahead.
 // The softmax's exponent offsets are computed once per row by one thread (1) or by every thread
 // from the four warps' maxima (0).
-#ifndef PA_ROW_OFFSETS
-#define PA_ROW_OFFSETS 1
-#endif
-#ifndef PA_KEEP_LOGITS
-#define PA_KEEP_LOGITS 1
-#endif
 #ifndef PA_ITEM_FROM_SLOT
 #define PA_ITEM_FROM_SLOT 1
 #endif
@@ -119,14 +113,7 @@ __host__ __device__ constexpr bool staged_token_scales(int block_size, bool per_
 __host__ __device__ constexpr int q_slot_bytes(int qr, bool staged_scales) {
   return q_tile_bytes(qr) + kQTokScales + (staged_scales ? 2 * kItemTokens * 4 : 0);
 }
-// P^T tile of one item: 8 k-steps x [row blocks of 8][2 K units][8 rows][16 tokens].  The strides
-// are padded off the 128-byte grid (k-step stride = 48 mod 128) so that byte stores of one warp
-// to different K units and k-steps fall into different banks.
-#ifndef PA_P_MN
-#define PA_P_MN 1
-#endif
-#if PA_P_MN
-// P^T as an MN-major operand: the 16 tile rows (N) of one token are 16 consecutive bytes, the
+// P^T tile of one item, an MN-major operand: the 16 tile rows (N) of one token are 16 consecutive bytes, the
 // tokens (K) of an 8-token core matrix are 16 bytes apart and core matrices follow one another,
 // so token t of the item sits at t * 16 and a softmax thread stores its token's bytes of a
 // chunk of rows with one vector store.  16-row items have a tile for the hi rows and one for the lo rows.
@@ -134,12 +121,6 @@ constexpr int kPLbo = 128;                          // between 8-token core matr
 constexpr int kPSbo = 4096;                         // between 16-row blocks (there is one per tile)
 __host__ __device__ constexpr int p_step_bytes(int) { return 512; }                     // a k-step: 32 tokens
 __host__ __device__ constexpr int p_tile_bytes(int qr) { return qr <= 8 ? 4096 : 8192; }
-#else
-constexpr int kPLbo = 144;                          // between the two K units of a k-step
-constexpr int kPSbo = 288;                          // between row blocks
-__host__ __device__ constexpr int p_step_bytes(int qr) { return qr <= 8 ? 560 : 1200; }
-__host__ __device__ constexpr int p_tile_bytes(int qr) { return 8 * p_step_bytes(qr) + 64; }
-#endif
 // TMEM columns of group g start at 4 * N * g: S^T (tg = 0 | 1) then O^T (parity 0 | 1), N each.
 __host__ __device__ constexpr int tmem_cols(int qr) { return 4 * acc_n(qr) * kNG <= 256 ? 256 : 512; }
 
@@ -1036,7 +1017,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA issue
     constexpr uint32_t kIdesc = idesc_f32acc(128, N, 0, 0);
-    constexpr uint32_t kIdescPV = idesc_f32acc(128, N, 0, 0, PA_P_MN != 0);   // P^T may be MN-major
+    constexpr uint32_t kIdescPV = idesc_f32acc(128, N, 0, 0, true);   // P^T is MN-major
     const bool leader = elect_one();  // the one lane that issues every MMA and commit
     // per item i: group g = i % NG, use gu = i / NG of the group's buffers, O^T parity gu & 1.
     // P.V of an item is issued kLag items after its QK^T, so a softmax group has that long to
@@ -1091,7 +1072,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           const uint64_t bd = pd + (uint64_t)((ks * kPStep) >> 4);
           if (leader) mma_f8_ss(d0, ad, bd, kIdescPV, ks > 0);
           if (kSum && leader)   // the lo rows' tile
-            mma_f8_ss(d0, ad, bd + (uint64_t)((PA_P_MN ? 4096 : QR / 8 * kPSbo) >> 4), kIdescPV, true);
+            mma_f8_ss(d0, ad, bd + (uint64_t)(4096 >> 4), kIdescPV, true);
         }
         if (leader) mma_commit(bar(kBarOFull, ob));
         __syncwarp();
@@ -1116,8 +1097,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
     uint32_t p_at[2];
 #pragma unroll
     for (int tg = 0; tg < 2; ++tg)
-      p_at[tg] = PA_P_MN ? p_tiles + grp * kPTile + tok[tg] * 16
-                         : p_tiles + grp * kPTile + (tok[tg] >> 5) * kPStep + ((tok[tg] >> 4) & 1) * kPLbo + (tok[tg] & 15);
+      p_at[tg] = p_tiles + grp * kPTile + tok[tg] * 16;
 
     // One chunk of RC rows of a transposed accumulator tile: value = hi column + lo column / 16.
     auto load_rows = [&](uint32_t tile, int ch, uint32_t (&h)[8], uint32_t (&l)[8]) {
@@ -1266,14 +1246,12 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
 #pragma unroll 1
       for (int ch = 0; ch < NCH; ++ch) {
         raw_logits(ch, s_keep);
-#if PA_KEEP_LOGITS
         // 16-row items: both chunks do not fit in registers, so the finished (scaled, masked) logits
         // go back into the accumulator columns they came from, and pass 2 reads them as they are
         if constexpr (kKeepInTmem) {
           tmem_st8(tmem_grp + ch * 8, s_keep[0]);
           tmem_st8(tmem_grp + N + ch * 8, s_keep[1]);
         }
-#endif
         float mx[RC];
 #pragma unroll
         for (int q = 0; q < RC; ++q) mx[q] = fmaxf(s_keep[0][q], s_keep[1][q]);
@@ -1291,7 +1269,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       }
       if (wq == 0) stamp(6, i, 1);
       named_barrier_sync(bar_a, 128);
-#if PA_ROW_OFFSETS
       // thread `row` of the group combines the four warps' maxima of its row, once for the group:
       // the exponent offset every thread applies in pass 2 (raw * factor - m * factor + 8 as one
       // multiply-add per element), and the row's maximum (base-2 logit domain) for the epilogue
@@ -1303,7 +1280,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         m_fin[par * 16 + r] = (m == -INFINITY || ALIBI) ? m : m * sc;
       }
       named_barrier_sync(bar_a, 128);
-#endif
       float vinv = 1.0f, vnorm = 1.0f;
       if (PER_TOKEN) {
         const float4 vm4 = *reinterpret_cast<const float4*>(v_max + grp * 4);
@@ -1319,9 +1295,7 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
         if (!wait(bar(kBarOFull, 2 * grp + (int)(pu & 1)), (pu >> 1) & 1)) return false;
       }
 
-#if PA_KEEP_LOGITS
       if constexpr (kKeepInTmem) tmem_st_wait();
-#endif
       if (wq == 0) stamp(6, i, 2);
       // ---- pass 2: P = exp2(raw * factor - m) * 256, split into hi / lo e4m3, stored as P^T
       // row sums of one chunk: lane ends up with the sum of one row over the warp's 64 tokens
@@ -1337,7 +1311,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
       float psum[RC];
 #pragma unroll 1
       for (int ch = 0; ch < NCH; ++ch) {
-#if PA_KEEP_LOGITS
         if constexpr (kKeepInTmem) {
           uint32_t a[8], b[8];
           tmem_ld8(tmem_grp + ch * 8, a);
@@ -1347,46 +1320,31 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
 #pragma unroll
           for (int q = 0; q < RC; ++q) s_keep[0][q] = __uint_as_float(a[q]), s_keep[1][q] = __uint_as_float(b[q]);
         } else
-#endif
         if (NCH > 1) raw_logits(ch, s_keep);  // recomputed rather than kept: registers
         uint32_t pbytes[2][2 * ((RC + 3) / 4)];  // [tg][hi words, lo words], row q = byte q % 4
         float hi[2][RC], lo[2][RC];
-#if PA_ROW_OFFSETS
         float offs[RC];
 #pragma unroll
         for (int q4 = 0; q4 < RC; q4 += 4) {
           const float4 o4 = *reinterpret_cast<const float4*>(row_off + grp * 16 + ch * RC + q4);
           offs[q4] = o4.x, offs[q4 + 1] = o4.y, offs[q4 + 2] = o4.z, offs[q4 + 3] = o4.w;
         }
-#endif
 #pragma unroll
         for (int q = 0; q < RC; ++q) {
-#if PA_ROW_OFFSETS
-          const float off_q = offs[q];
-#else
-          const float4 m4 = *reinterpret_cast<const float4*>(rm + (ch * RC + q) * 4);
-          const float m = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w));
-          const float off_q = (m == -INFINITY) ? 8.0f : (ALIBI ? 8.0f - m : fmaf(-m, row_scale[q], 8.0f));
-#endif
           // exponent argument raw * factor - m * factor + 8 as one multiply-add per element
           float p0, p1;
           if (ALIBI) {   // s_keep holds finished logits
-            const float off = off_q;
-            p0 = ex2(s_keep[0][q] + off);
-            p1 = ex2(s_keep[1][q] + off);
+            p0 = ex2(s_keep[0][q] + offs[q]);
+            p1 = ex2(s_keep[1][q] + offs[q]);
           } else {
-            const float off = off_q;
-            p0 = ex2(fmaf(s_keep[0][q], row_scale[q], off));
-            p1 = ex2(fmaf(s_keep[1][q], row_scale[q], off));
+            p0 = ex2(fmaf(s_keep[0][q], row_scale[q], offs[q]));
+            p1 = ex2(fmaf(s_keep[1][q], row_scale[q], offs[q]));
           }
           psum[q] = p0 + p1;
           split_parts<kSum>(PER_TOKEN ? p0 * vs_tok[0] : p0, hi[0][q], lo[0][q]);
           split_parts<kSum>(PER_TOKEN ? p1 * vs_tok[1] : p1, hi[1][q], lo[1][q]);
         }
         constexpr int W = (RC + 3) / 4;
-        // tile rows: hi half at row ch * RC + q, lo half at row QR + ch * RC + q
-        const uint32_t hi_at = RC == 8 ? ch * kPSbo : 0;
-        const uint32_t lo_at = RC == 8 ? (QR / 8 + ch) * kPSbo : QR * 16;
 #pragma unroll
         for (int tg = 0; tg < 2; ++tg) {
 #pragma unroll
@@ -1394,7 +1352,6 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
             pbytes[tg][w] = pack_e4m3x4(hi[tg][4 * w], hi[tg][4 * w + 1], hi[tg][4 * w + 2], hi[tg][4 * w + 3]);
             pbytes[tg][W + w] = pack_e4m3x4(lo[tg][4 * w], lo[tg][4 * w + 1], lo[tg][4 * w + 2], lo[tg][4 * w + 3]);
           }
-#if PA_P_MN
           // tile row n of the token is byte n of its 16: hi rows at q, lo rows at QR + q (their own tile with 16 rows)
           if constexpr (RC == 4) {
             sts64(p_at[tg], pbytes[tg][0], pbytes[tg][1]);
@@ -1402,22 +1359,8 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
             sts64(p_at[tg] + ch * 8, pbytes[tg][0], pbytes[tg][1]);
             sts64(p_at[tg] + (QR == 16 ? 4096 + ch * 8 : 8), pbytes[tg][2], pbytes[tg][3]);
           }
-#else
-#pragma unroll
-          for (int q = 0; q < RC; ++q) {
-            sts8(p_at[tg] + hi_at + q * 16, pbytes[tg][q >> 2] >> (8 * (q & 3)));
-            sts8(p_at[tg] + lo_at + q * 16, pbytes[tg][W + (q >> 2)] >> (8 * (q & 3)));
-          }
-#endif
         }
         if (NCH > 1) row_sums(ch, psum);
-      }
-      // thread `row` of the group keeps the row's maximum (base-2 logit domain) for the epilogue
-      if (!PA_ROW_OFFSETS && r < QR) {
-        const float4 m4 = *reinterpret_cast<const float4*>(rm + r * 4);
-        const float m = fmaxf(fmaxf(m4.x, m4.y), fmaxf(m4.z, m4.w));
-        const float sc = __uint_as_float(lds32(aux + r * 4));
-        m_fin[par * 16 + r] = (m == -INFINITY || ALIBI) ? m : m * sc;
       }
       __syncwarp();   // the query slot's scales were read until here
       if (lane == 0) mbar_arrive(bar(kBarQEmpty, slot));
