@@ -552,7 +552,14 @@ int launch_reduce(const PaDecodeParams* p, float* tri_m, float* tri_l, float* tr
   // one warp per row while a row has at most one chunk of 32 partitions (four rows per CTA); up to
   // four chunks: eight rows per CTA whose further chunks are dealt over the CTA's warps; beyond
   // that sixteen warps per row
-  const int wpr = r.max_partitions <= 32 ? 1 : (r.max_partitions <= 32 * pa::kMidChunks ? 4 : 16);
+  // (the eight-row form only where its CTAs are many: a few long rows, e.g. one GPU's share of a long
+  // context split over eight GPUs, are latency-bound and want a CTA each -- 15.6 against 22.9 us per call
+  // for 64 rows of 64 partitions; a thousand rows of 40 partitions: 107 us against 125 the other way round)
+  DeviceInfo* dev = nullptr;
+  const int rc_dev = device_info(&dev);
+  if (rc_dev != PA_OK) return rc_dev;
+  const bool many_rows = rows >= (int64_t)4 * dev->sm_count;   // eight-row CTAs on half of the SMs at least
+  const int wpr = r.max_partitions <= 32 ? 1 : (r.max_partitions <= 32 * pa::kMidChunks && many_rows ? 4 : 16);
   const int64_t blocks = wpr == 16 ? rows : (wpr == 4 ? (rows + pa::kMidRows - 1) / pa::kMidRows : (rows + 3) / 4);
   if (blocks > 0x7fffffff) return PA_ERR_TOO_LARGE;
   // Programmatic dependent launch: the reduce grid may be scheduled while the partition kernel
