@@ -40,7 +40,9 @@
 //   warp 13/14   K / V producers (bulk copies; page ids prefetched an item ahead).  Issuing a bulk
 //                copy costs a warp 75-90 cycles and the copies of one warp go out one after the
 //                other, so the 16 + 16 copies of an item need two warps.
-//   warp 15      query producer: bf16 -> hi/lo e4m3 tile in the B-operand layout, per-token scales
+//   warp 15      query producer: bf16 -> hi/lo e4m3 tile in the B-operand layout, the rows' factors, and
+//                what else the softmax groups need per item (the item itself; the item's per-token
+//                scales by bulk copy where a page's scales are contiguous): see q_slot_bytes
 // K and V have their own rings of 32 KB slots.  Every wait is bounded and reports
 // PA_DEV_WAIT_TIMEOUT.
 #pragma once
@@ -1116,9 +1118,10 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
                      : fmaf(__uint_as_float(l[q]), 0.0625f, __uint_as_float(h[q]));
     };
 
-    // Per-token K / V scales of this lane's two tokens come straight from global memory, fetched
-    // ahead by the group itself: the block-table entry two of the group's items ahead, the four
-    // scales one item ahead (each step has a whole group iteration to land).
+    // Unless they are staged in the query slot (kStaged), per-token K / V scales of this lane's two
+    // tokens come straight from global memory, fetched ahead by the group itself: the block-table
+    // entry two of the group's items ahead, the four scales one item ahead (each step has a whole
+    // group iteration to land).
     auto load_tok_pids = [&](const TcItem& it, int (&pid)[2]) {
       pid[0] = 0;
       pid[1] = 0;
