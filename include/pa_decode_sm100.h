@@ -101,7 +101,7 @@ typedef struct PaDecodeParams {
   int32_t* status;             /* optional device int32, OR-ed with PA_DEV_* bits */
   uint64_t* trace;             /* optional tuning aid: device buffer of PA_TRACE_WORDS uint64 that
                                 * receives SM-clock stamps of CTA 0's pipeline roles; NULL normally.
-                                * Only a library built with -DPA_TRACE_BUILD writes it (16-token pages);
+                                * Only a library built with -DPA_TRACE_BUILD writes it (pages of 16 or 1024 tokens);
                                 * the default build ignores it. */
   int32_t* merge_counters;     /* optional [S*Hkv] device int32, ZERO before the first call and left zero by
                                 * every call that completes.  With it and tune_fuse = 1, pa_decode_sm100 runs as

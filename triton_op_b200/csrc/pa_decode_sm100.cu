@@ -472,12 +472,16 @@ int launch_partition(const LaunchPlan& plan, cudaStream_t stream) {
   if (plan.tensor_path) {
     switch (plan.kp.block_size) {
       case 16:
-#ifdef PA_TRACE_BUILD   // tuning builds (-DPA_TRACE_BUILD): clock stamps compiled in, this page size only
+#ifdef PA_TRACE_BUILD   // tuning builds (-DPA_TRACE_BUILD): clock stamps compiled in (pages of 16 and of 1024 tokens)
         if (plan.kp.trace != nullptr) return launch_tensor_bs<16, true>(plan, stream);
 #endif
         return launch_tensor_bs<16, false>(plan, stream);
       case 64: return launch_tensor_bs<64, false>(plan, stream);
-      case 1024: return launch_tensor_bs<1024, false>(plan, stream);
+      case 1024:
+#ifdef PA_TRACE_BUILD
+        if (plan.kp.trace != nullptr) return launch_tensor_bs<1024, true>(plan, stream);
+#endif
+        return launch_tensor_bs<1024, false>(plan, stream);
       default: return PA_ERR_UNSUPPORTED;
     }
   }
