@@ -347,6 +347,24 @@ def test_single_launch_decode_with_sets_cut_in_many_places(shape):
     assert int(get_merge_counters(res["temporary_output"], S, hkv).abs().sum().item()) == 0
 
 
+@pytest.mark.parametrize("bs,ql,quant", [(64, 1, "per_token"), (1024, 2, "per_token"), (1024, 1, "per_tensor"), (64, 2, "per_tensor")])
+def test_single_launch_decode_with_long_pages(bs, ql, quant):
+    """The single-launch form on pages of 64 and 1024 tokens, with the per-token scales staged in the
+    query slots: bit-identical to the two-launch form, counters back at zero."""
+    from triton_op_b200.inputs import DecodeConfig, make_inputs
+    from triton_op_b200.pa_decode import get_merge_counters
+    cfg = DecodeConfig("fuse_pages", 30, 8, 4, bs, ql, ("uniform", 1, 3000), quant=quant)
+    inp = make_inputs(cfg, seed=bs + ql, device=DEV)
+    two, _ = run_operator(inp)
+    st = _status()
+    for _ in range(2):
+        one, res = run_operator(inp, status=st, tune={"fuse": 1})
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert torch.equal(one.view(torch.int16), two.view(torch.int16))
+    assert int(get_merge_counters(res["temporary_output"], 30, 4).abs().sum().item()) == 0
+
+
 @pytest.mark.parametrize("form", ["two launches", "single launch", "partition 512"])
 def test_lengths_and_tables_written_by_the_kernel_just_before_the_call(form):
     """The tcgen05 kernel builds its partition index before its dependency wait and checks it after
