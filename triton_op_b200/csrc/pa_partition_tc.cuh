@@ -780,13 +780,18 @@ pa_partition_fp8_tc_kernel(const __grid_constant__ KernelParams p, const __grid_
           if (pg < npg) bulk_g2s(dst + c * 4096 + pg * 1024, src + c * 1024, 1024, full, pol);
         }
       } else {               // 256-token slice of one large page
+        // only what holds a token of the context is fetched (the last partition of a sequence): rows
+        // of the K tile past it keep older bytes, whose logits are masked, and the softmax clears the
+        // V slot past the context whether it was loaded or not
         const int tin = it.tok0 % BS;
-        if (lane == 0) mbar_arrive_expect_tx(full, kHalfSlot);
+        const int boxes = it.ntok > 128 ? 2 : 1;
+        const uint32_t kbytes = (uint32_t)it.ntok * 16;
+        if (lane == 0) mbar_arrive_expect_tx(full, is_v ? (uint32_t)(boxes * G::kVBox) : 8 * kbytes);
         __syncwarp();
-        if (is_v) {          // two swizzled boxes [128 d][128 tok]
-          if (lane < 2) tma_load_4d(dst + lane * G::kVBox, &vmap, tin + 128 * lane, 0, it.head, pid, full, pol);
-        } else if (lane < 8) {  // 8 chunks x (256 tok x 16 B)
-          bulk_g2s(dst + lane * 4096, src + (int64_t)lane * BS * 16 + tin * 16, 4096, full, pol);
+        if (is_v) {          // swizzled boxes [128 d][128 tok]
+          if (lane < boxes) tma_load_4d(dst + lane * G::kVBox, &vmap, tin + 128 * lane, 0, it.head, pid, full, pol);
+        } else if (lane < 8) {  // 8 chunks x (tokens x 16 B)
+          bulk_g2s(dst + lane * 4096, src + (int64_t)lane * BS * 16 + tin * 16, kbytes, full, pol);
         }
       }
       stamp(is_v ? 1 : 0, i, 2);
